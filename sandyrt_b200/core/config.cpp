@@ -236,6 +236,15 @@ std::map<std::string, Architecture>& table() {
             return describe_sovezen(*g);
         };
         t[sovezen.name] = std::move(sovezen);
+        Architecture bilurax;
+        bilurax.name = BiluraxConfig::kArchitecture;
+        bilurax.parse = [](const Json& raw) { return std::unique_ptr<ModelConfig>(new BiluraxConfig(BiluraxConfig::from_json(raw))); };
+        bilurax.describe = [](const ModelConfig& c) {
+            const auto* g = dynamic_cast<const BiluraxConfig*>(&c);
+            if (!g) throw ConfigError("Bilurax was given another architecture's configuration");
+            return describe_bilurax(*g);
+        };
+        t[bilurax.name] = std::move(bilurax);
     });
     return t;
 }

@@ -113,6 +113,35 @@ public:
     int owner(int layer) const;                             // the layer whose tensors `layer` uses (itself, mostly)
 };
 
+// Bilurax's config.json (core/bilurax.cpp says what the keys mean): layers listed one by one, each an attention with
+// normed queries, keys and values, capped scores and chunks of positions, behind a token shift; a dense or routed
+// feed-forward, or none; a span of layers that may run several times.
+class BiluraxConfig : public ModelConfig {
+public:
+    static constexpr const char* kArchitecture = "Bilurax";
+    struct Layer {
+        std::string type;                                   // "attention"
+        int64_t heads = 0, kv_heads = 0, dim = 0, vdim = 0;
+        double scale = 1.0, softcap = 0.0;
+        int64_t chunk = 0;                                  // mask.size: a query sees the keys of its own chunk of positions
+        std::string mlp;                                    // "dense" | "moe" | "" (no feed-forward)
+        int64_t ff = 0;                                     // dense: inner size; moe: an expert's inner size
+        double limit = 0.0;                                 // moe: where an expert's gate and up values are cut off
+        int64_t experts = 0, top = 0, groups = 1, keep = 1;
+        double router_scale = 1.0;
+    };
+    int64_t vocab = 0, width = 0;
+    double norm_eps = 1e-6, logit_softcap = 0.0, embedding_scale = 1.0;
+    std::vector<Layer> layers;
+    bool has_loop = false;
+    int64_t loop_start = 0, loop_stop = 0, loop_times = 1;
+
+    static BiluraxConfig from_json(const Json& raw);
+    std::string architecture() const override { return kArchitecture; }
+    Json to_json() const override;
+    void validate() const override;
+};
+
 // A configuration of an architecture defined outside this library: its normalised config.json
 // as the architecture's own `parse` returned it.
 class ForeignConfig : public ModelConfig {
@@ -148,5 +177,6 @@ ModelSpec describe(const ModelConfig& cfg);
 ModelSpec describe_gpt2(const GPT2Config& cfg);
 ModelSpec describe_panupel(const PanupelConfig& cfg);
 ModelSpec describe_sovezen(const SovezenConfig& cfg);
+ModelSpec describe_bilurax(const BiluraxConfig& cfg);
 
 }  // namespace sandy

@@ -96,6 +96,7 @@ Act act_from_name(const std::string& name) {
     if (name.empty() || name == "none") return Act::None;
     if (name == "gelu_new" || name == "gelu_tanh") return Act::GeluNew;
     if (name == "gelu" || name == "gelu_erf") return Act::Gelu;
+    if (name == "relu_squared") return Act::ReluSquared;
     throw ValueError("unknown activation '" + name + "'");
 }
 
@@ -481,6 +482,10 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     (void)ws;
     const float* sk = extras ? extras->sink : nullptr;
     const float* og = extras ? extras->out_gate : nullptr;
+    const float cap = extras ? extras->softcap : 0.0f;
+    const int chunk = extras ? extras->chunk : 0;
+    if (cap < 0.0f || chunk < 0) throw UnsupportedShape("attention: softcap and chunk must not be negative");
+    const bool ruled = cap > 0.0f || chunk > 0;           // only kernels with a form for these rules take such steps
     const int d = c.head_dim, hkv = c.n_kv_heads;
     if (d % 16 != 0 || d > kMaxHeadDim) throw UnsupportedShape("attention: head size " + std::to_string(d) + " must be a multiple of 16, at most " + std::to_string(kMaxHeadDim));
     if (hkv <= 0 || n_heads % hkv != 0)
@@ -492,7 +497,7 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     const double attn_bytes = 2.0 * s.kv_tokens * hkv * d * q.elem_size() + 2 * tensor_bytes(&q);
     const double attn_flops = 4.0 * s.pairs * n_heads * d;
     const std::string shape = "(H=" + std::to_string(n_heads) + ",Hkv=" + std::to_string(hkv) + ",D=" + std::to_string(d) + ")";
-    if (s.max_q_len > 1 && q.dtype == DType::BF16 && d <= 128) {
+    if (s.max_q_len > 1 && q.dtype == DType::BF16 && d <= 128 && !ruled) {
         static const bool use_tc = env_int("SANDYRT_PREFILL_TC", 1) != 0;     // 0 keeps every head size on the mma.sync kernel
         if (use_tc && d == 64) {
             static auto fn = SANDY_KERNEL(attention_prefill_tc, sandy_prefill_attention_tc_ext);
@@ -517,7 +522,7 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     // It is two launches with a floor of 9 us, so it takes the steps with enough (token, head, key) triples.  Alone, 12
     // heads of 128 on one key/value head, us, this kernel / the best of the kernels below: 1 token x 392 keys 9.1 / 5.2;
     // 8 x 392: 9.4 / 8.7; 8 tokens x 24 heads x 392: 11.3 / 16.6; 8 x 12 x 2,000: 13.2 / 36.2.
-    if (s.max_q_len == 1 && q.dtype == DType::BF16 && d <= 128 && n_heads / hkv >= kSharedKvMinHeads && T <= 65535 &&
+    if (!ruled && s.max_q_len == 1 && q.dtype == DType::BF16 && d <= 128 && n_heads / hkv >= kSharedKvMinHeads && T <= 65535 &&
         (int64_t)T * n_heads * s.max_blocks * c.page_size >= kSharedKvMinTriples) {
         const int max_kv = s.max_blocks * c.page_size;
         const int tiles = hkv * ((n_heads / hkv + 15) / 16), groups = (max_kv + 15) / 16;
@@ -532,7 +537,7 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
               "decode_attention_shared" + shape);
         return;
     }
-    if (s.max_q_len == 1 && decode_head_dim(q.dtype, d)) {
+    if (!ruled && s.max_q_len == 1 && decode_head_dim(q.dtype, d)) {
         const int max_kv = s.max_blocks * c.page_size;
         const int splits = std::min(decode_splits(T, n_heads, max_kv), kClusterMaxSplits);
         const size_t stage = 2 * (size_t)c.page_size * (size_t)d * q.elem_size();
@@ -581,10 +586,11 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
         }
         return;
     }
-    static auto fn = SANDY_KERNEL(attention, sandy_paged_attention_ext);
+    static auto fn = SANDY_KERNEL(attention, sandy_paged_attention_cap);
     OpTimer timer(l, "attention, general", attn_bytes, attn_flops);
     check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.token_seq, s.positions, out.data,
-             (int)out.ld, T, n_heads, hkv, d, c.page_size, scale, window, c.num_pages, code_of(q.dtype), sk, og, l.kernel_status, l.stream),
+             (int)out.ld, T, n_heads, hkv, d, c.page_size, scale, window, cap, chunk, c.num_pages, code_of(q.dtype), sk, og,
+             l.kernel_status, l.stream),
           "paged_attention" + shape);
 }
 
@@ -599,6 +605,30 @@ void rmsnorm(const Launch& l, const Tensor& x, const Tensor* gain, float eps, Te
     check(fn((const float*)x.data, (int)x.ld, gain ? (const float*)gain->data : nullptr, out.data, (int)out.ld, rows, n_rows,
              (int)x.cols, eps, code_of(out.dtype), l.stream),
           "rmsnorm(width=" + std::to_string(x.cols) + ")");
+}
+
+void rmsnorm_shift(const Launch& l, const StepSeqs& s, const Tensor& x, const Tensor* gain, float eps, const Tensor& mix,
+                   const StateView& state, Tensor& out, int max_q_len) {
+    if (x.dtype != DType::F32 || (gain && (gain->dtype != DType::F32 || gain->numel() != x.cols)) || mix.dtype != DType::F32 ||
+        mix.numel() != x.cols || out.rows != x.rows || out.cols != x.cols || state.dtype != DType::F32 || state.row_elems < x.cols ||
+        x.rows != s.n_tokens)
+        throw KernelError("rmsnorm_shift: float32 x [T, width], gain and mix [width], a float32 state of at least width floats expected");
+    if (left_out("layernorm")) return;
+    static auto fn = SANDY_KERNEL(rmsnorm, sandy_rmsnorm_shift);
+    static auto keep = SANDY_KERNEL(rmsnorm, sandy_rmsnorm_keep);
+    const float* g = gain ? (const float*)gain->data : nullptr;
+    {
+        OpTimer timer(l, "rmsnorm + token shift", (double)x.rows * x.cols * (2 * x.elem_size() + out.elem_size()), 0);
+        check(fn((const float*)x.data, (int)x.ld, g, (const float*)mix.data, (float*)state.data, (long long)state.row_elems,
+                 s.token_seq, s.q_start, s.seq_slots, out.data, (int)out.ld, s.n_tokens, (int)x.cols, eps, code_of(out.dtype), l.stream),
+              "rmsnorm_shift(width=" + std::to_string(x.cols) + ")");
+    }
+    if (max_q_len > 1) {
+        OpTimer timer(l, "token shift: last rows kept", 2.0 * s.n_seqs * x.cols * sizeof(float), 0);
+        check(keep((const float*)x.data, (int)x.ld, g, (float*)state.data, (long long)state.row_elems, s.q_start, s.seq_slots, s.n_seqs,
+                   (int)x.cols, eps, l.stream),
+              "rmsnorm_keep");
+    }
 }
 
 void rmsnorm_add(const Launch& l, const Tensor& y, const Tensor* gain, float eps, float mult, Tensor& x) {
@@ -637,6 +667,34 @@ void glu(const Launch& l, const Tensor& a, const Tensor& b, GluAct act, Tensor& 
     static auto fn = SANDY_KERNEL(elementwise, sandy_glu);
     OpTimer timer(l, "gated activation", 3.0 * tensor_bytes(&out), 0);
     check(fn(a.data, b.data, (int)a.ld, out.data, (int)out.ld, (int)a.rows, (int)a.cols, (int)act, code_of(a.dtype), l.stream), "glu");
+}
+
+void glu_clamped(const Launch& l, const Tensor& a, const Tensor& b, float limit, float alpha, Tensor& out) {
+    if (a.dtype != b.dtype || a.dtype != out.dtype || a.rows != b.rows || a.cols != b.cols || a.ld != b.ld || out.rows != a.rows ||
+        out.cols != a.cols)
+        throw KernelError("glu_clamped: a, b and out must agree in shape and type");
+    static auto fn = SANDY_KERNEL(elementwise, sandy_glu_clamped);
+    OpTimer timer(l, "gated activation", 3.0 * tensor_bytes(&out), 0);
+    check(fn(a.data, b.data, (int)a.ld, out.data, (int)out.ld, (int)a.rows, (int)a.cols, limit, alpha, code_of(a.dtype), l.stream),
+          "glu_clamped");
+}
+
+void stream_add(const Launch& l, Tensor& x, const Tensor* x0, const Tensor* row) {
+    if (x.dtype != DType::F32 || (x0 && (x0->dtype != DType::F32 || x0->rows != x.rows || x0->cols != x.cols)) ||
+        (row && (row->dtype != DType::F32 || row->numel() != x.cols)))
+        throw KernelError("stream_add: float32 x and x0 of one shape, a float32 row [width] expected");
+    static auto fn = SANDY_KERNEL(elementwise, sandy_stream_add);
+    OpTimer timer(l, "stream + embedding + row", (x0 ? 3.0 : 2.0) * tensor_bytes(&x), 0);
+    check(fn((float*)x.data, (int)x.ld, x0 ? (const float*)x0->data : nullptr, x0 ? (int)x0->ld : 0,
+             row ? (const float*)row->data : nullptr, (int)x.rows, (int)x.cols, l.stream),
+          "stream_add");
+}
+
+void softcap(const Launch& l, Tensor& x, float cap) {
+    if (x.dtype != DType::F32 || !x.contiguous()) throw KernelError("softcap: a dense float32 tensor expected");
+    static auto fn = SANDY_KERNEL(elementwise, sandy_softcap_f32);
+    OpTimer timer(l, "softcap", 2.0 * tensor_bytes(&x), 0);
+    check(fn((float*)x.data, (long long)x.numel(), cap, l.stream), "softcap");
 }
 
 void cast_cols(const Launch& l, const Tensor& x, Tensor& out) {
@@ -715,6 +773,24 @@ void moe_route(const Launch& l, const Tensor& logits, const Tensor* bias, const 
     check(group(r.expert_of, r.n_tokens * r.top, r.n_experts, r.group_start, r.entry_of_slot, r.slot_of_entry, l.stream), "moe_group");
 }
 
+void moe_route_scored(const Launch& l, const Tensor& logits, const Tensor* correction, const ScoredRoute& rule, const Routing& r) {
+    if (logits.dtype != DType::F32 || logits.rows != r.n_tokens || logits.cols != r.n_experts ||
+        (correction && (correction->dtype != DType::F32 || correction->numel() != r.n_experts)))
+        throw KernelError("moe_route_scored: float32 logits [tokens, experts] and a float32 correction [experts] expected");
+    static auto route = SANDY_KERNEL(moe, sandy_moe_route_scored);
+    static auto group = SANDY_KERNEL(moe, sandy_moe_group);
+    {
+        OpTimer timer(l, "expert routing", tensor_bytes(&logits), 0);
+        check(route((const float*)logits.data, (int)logits.ld, correction ? (const float*)correction->data : nullptr, r.n_tokens,
+                    r.n_experts, r.top, rule.n_groups, rule.keep_groups, rule.group_rank, rule.weight_scale, rule.norm_eps, r.expert_of,
+                    r.weight_of, l.stream),
+              "moe_route_scored(E=" + std::to_string(r.n_experts) + ",top=" + std::to_string(r.top) + ",groups=" +
+                  std::to_string(rule.n_groups) + ")");
+    }
+    OpTimer timer(l, "expert grouping", 12.0 * r.n_tokens * r.top, 0);
+    check(group(r.expert_of, r.n_tokens * r.top, r.n_experts, r.group_start, r.entry_of_slot, r.slot_of_entry, l.stream), "moe_group");
+}
+
 void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gather, const Tensor& w, ExpertAct act, Tensor& out,
                     Tensor* sorted) {
     if (r.n_experts <= 0 || w.rows % r.n_experts) throw KernelError("expert_product: the weight's rows do not divide into the experts");
@@ -771,12 +847,12 @@ void attention_prepare(const Launch& l, const AttentionPrepare& p, const Tensor&
     if (proj.dtype != c.dtype || q_out.dtype != proj.dtype || q_out.rows != proj.rows || q_out.cols != (int64_t)p.n_heads * c.head_dim ||
         c.n_kv_heads != p.n_kv_heads || c.head_dim < p.qk_dim || c.head_dim < p.v_dim)
         throw KernelError("attention_prepare: the projection, the queries and the cache disagree");
-    static auto fn = SANDY_KERNEL(attention_prepare, sandy_attention_prepare);
+    static auto fn = SANDY_KERNEL(attention_prepare, sandy_attention_prepare_ext);
     OpTimer timer(l, "q/k norm + rotary + cache write", 2.0 * tensor_bytes(&proj), 0);
     check(fn(proj.data, (int)proj.ld, p.q_off, p.k_off, p.v_off, (int)proj.rows, p.n_heads, p.n_kv_heads, p.qk_dim, p.v_dim,
              c.head_dim, p.q_gain, p.k_gain, p.eps, p.freq, p.rot_dims, positions, token_seq, block_table, max_blocks, c.k, c.v,
              c.page_stride, c.page_size, c.num_pages, p.write_cache ? 1 : 0, q_out.data, (int)q_out.ld, p.gate_in, p.ld_gate,
-             p.gate_out, p.gate_scale, code_of(proj.dtype), l.kernel_status, l.stream),
+             p.gate_out, p.gate_scale, p.q_head_scale, p.v_unit_eps, code_of(proj.dtype), l.kernel_status, l.stream),
           "attention_prepare");
 }
 

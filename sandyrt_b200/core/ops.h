@@ -19,8 +19,8 @@
 namespace sandy {
 namespace ops {
 
-enum class Act : int { None = 0, GeluNew = 1, Gelu = 2 };
-Act act_from_name(const std::string& name);          // "gelu_new" / "gelu_tanh" / "gelu" / "gelu_erf" / "none"
+enum class Act : int { None = 0, GeluNew = 1, Gelu = 2, ReluSquared = 3 };
+Act act_from_name(const std::string& name);          // "gelu_new" / "gelu_tanh" / "gelu" / "gelu_erf" / "relu_squared" / "none"
 
 // Where the launches of one step go and where kernels report trouble.
 struct Launch {
@@ -130,9 +130,14 @@ struct AttentionStep {
 };
 // What some attention layers add to the softmax: a sink per head (float32 [H]: exp(sink) joins the denominator and
 // nothing else) and a factor on each head's output (float32 [T, H], e.g. a sigmoid gate).  Either may be null.
+// Two rules on the scores: `softcap` > 0 presses a score into softcap * tanh(score / softcap) before the softmax;
+// `chunk` > 0 lets a query at position pos see only the keys of its own chunk, j >= pos - pos % chunk (chunks are counted
+// from position 0 of the request).  Kernels without a form for a rule leave such steps to those that have one.
 struct AttentionExtras {
     const float* sink = nullptr;
     const float* out_gate = nullptr;
+    float softcap = 0.0f;
+    int chunk = 0;
 };
 // The widest head any attention kernel takes (the general kernel; the tensor-core prompt kernels take up to 128, the
 // decode kernels 16 / 32 / 64 / 128 and, in bfloat16, 256).
@@ -147,8 +152,20 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
 int decode_splits(int n_tokens, int n_heads, int max_kv, int sms = 0);
 
 // ---- RMS norms and what goes with them (rmsnorm.cu, elementwise.cu) ------------------------------------------
+struct StepSeqs {                                                  // the step's requests, as kernels with a state per request need them
+    int n_tokens = 0, n_seqs = 0;
+    const int* token_seq = nullptr;
+    const int* q_start = nullptr;
+    const int* seq_slots = nullptr;
+};
 // out[r] = x[rows[r] or r] / sqrt(mean(x^2) + eps) * gain; x float32, gain float32 [width] or null.
 void rmsnorm(const Launch& l, const Tensor& x, const Tensor* gain, float eps, Tensor& out, const int* rows, int n_rows);
+// Token shift behind the norm: h[t] = norm(x[t]) * gain, out[t] = h[t] + (h[t-1] - h[t]) * mix, where the h before a
+// request's first token of the step is the first x.cols floats of its state row (zeros at a request's very first
+// token: a slot is cleared on admission), and the row then takes the h of the request's last token.  All 32-bit; out
+// in its own type.  `max_q_len` is the step's longest portion (one launch when it is 1, two otherwise).
+void rmsnorm_shift(const Launch& l, const StepSeqs& s, const Tensor& x, const Tensor* gain, float eps, const Tensor& mix,
+                   const StateView& state, Tensor& out, int max_q_len);
 // x += mult * y / sqrt(mean(y^2) + eps) * gain; both float32.
 void rmsnorm_add(const Launch& l, const Tensor& y, const Tensor* gain, float eps, float mult, Tensor& x);
 enum class GateAct : int { Sigmoid = 0, Silu = 1 };
@@ -159,6 +176,8 @@ void head_norm_gate(const Launch& l, const Tensor& o, const Tensor* gain, const 
 enum class GluAct : int { Silu = 0, GeluTanh = 1 };
 // out = act(a) * b, element by element (a and b may be column ranges of one matrix).
 void glu(const Launch& l, const Tensor& a, const Tensor& b, GluAct act, Tensor& out);
+// out = g * sigmoid(alpha * g) * (u + 1) with g = min(a, limit), u = clamp(b, -limit, limit), element by element.
+void glu_clamped(const Launch& l, const Tensor& a, const Tensor& b, float limit, float alpha, Tensor& out);
 // out = x rounded to out's type (out may be a column range of a wider matrix); x float32.
 void cast_cols(const Launch& l, const Tensor& x, Tensor& out);
 
@@ -166,6 +185,10 @@ void cast_cols(const Launch& l, const Tensor& x, Tensor& out);
 void scale_add(const Launch& l, const Tensor& y, const Tensor& gain, const Tensor* y2, const Tensor* gain2, Tensor& x);
 // x *= s, float32 (logits times a constant).
 void scale(const Launch& l, Tensor& x, float s);
+// x += x0 + row: x and x0 float32 [T, width], row float32 [width]; x0 and row may each be null.
+void stream_add(const Launch& l, Tensor& x, const Tensor* x0, const Tensor* row);
+// x = cap * tanh(x / cap), float32 (logits pressed into (-cap, cap)).
+void softcap(const Launch& l, Tensor& x, float cap);
 
 // ---- attention over a latent (latent_prepare.cu, grouped_gemm.cu) ---------------------------------------------
 // What the cache of such a layer holds per token, [latent | shared rotated key part | zeros], is key and value at
@@ -201,6 +224,14 @@ struct Routing {
 };
 // logits float32 [T, E] (+ bias float32 [E] or null) -> the routing's arrays.
 void moe_route(const Launch& l, const Tensor& logits, const Tensor* bias, const Routing& r);
+// Routing by scores: s = sigmoid(logit); the choice is by s + correction among the experts of the `keep_groups` best of
+// `n_groups` equal groups of neighbours (a group's score: the sum of its `group_rank` largest choice scores); the weights
+// are the chosen s over their sum (+ norm_eps), times weight_scale.
+struct ScoredRoute {
+    int n_groups = 1, keep_groups = 1, group_rank = 2;
+    float weight_scale = 1.0f, norm_eps = 0.0f;
+};
+void moe_route_scored(const Launch& l, const Tensor& logits, const Tensor* correction, const ScoredRoute& rule, const Routing& r);
 enum class ExpertAct : int { None = 0, ReluSquared = 1 };
 // out[s] = act(W_e a[row(s)]) for the slots s of every expert e; w [E * N, K]; with `gather` a slot reads its token's
 // row of `a` ([T, K]), else row s ([T * top, K]).  out [T * top, N].
@@ -229,6 +260,8 @@ struct AttentionPrepare {
     int ld_gate = 0;
     float* gate_out = nullptr;                                     // float32 [T, H]: sigmoid(gate_in) * gate_scale
     float gate_scale = 1.0f;
+    const float* q_head_scale = nullptr;                           // float32 [H]: a factor on each query head, or null
+    float v_unit_eps = 0.0f;                                       // > 0: every value head over its root mean square (this eps)
     bool write_cache = true;
 };
 void attention_prepare(const Launch& l, const AttentionPrepare& p, const Tensor& proj, const KVView& cache,
@@ -238,12 +271,6 @@ void attention_prepare(const Launch& l, const AttentionPrepare& p, const Tensor&
 // Columns of a head's state that one thread block owns; the matrix memory keeps n and m once per such block.
 constexpr int kMatrixStateCols = SANDY_MATRIX_STATE_COLS;
 int64_t mlstm_state_floats(int n_heads, int qk_dim, int v_dim);
-struct StepSeqs {                                                  // the step's requests, as the recurrences need them
-    int n_tokens = 0, n_seqs = 0;
-    const int* token_seq = nullptr;
-    const int* q_start = nullptr;
-    const int* seq_slots = nullptr;
-};
 struct DeltaShape { int n_heads = 0, n_qk_heads = 0, qk_dim = 0, v_dim = 0, n_taps = 0; };
 // conv + silu + unit vectors + gates.  proj [T, >= channels] (q, k, v channels first); taps float32 [channels, n_taps];
 // gates float32 [T, 2H] (beta's pre-activation, then the decay's); qkv float32 [T, channels]; bg float32 [T, 2H]

@@ -42,6 +42,12 @@ bool NormedInput::fusable(ops::FusedNorm& out) const {
     return true;
 }
 
+bool NormedInput::rms(RmsNormParams& out) const {
+    if (!norm_.rms_params(out)) return false;
+    out.x = x_;
+    return true;
+}
+
 // ---- Linear ----------------------------------------------------------------------------------------------
 Linear::Linear(int64_t in_features, int64_t out_features, bool bias, const std::string& layout, std::string name)
     : in_(in_features), out_(out_features), has_bias_(bias), w_out_in_(layout == "out_in"), layout_(layout), name_(std::move(name)) {
@@ -184,10 +190,12 @@ public:
 };
 
 // Token embedding: x[t] = table[id[t]] (+ position table[pos[t]] when the position encoding has one),
-// one fused pass (src/models/gpt2_small.sandy.go:48-50 of the reference).
+// one fused pass (src/models/gpt2_small.sandy.go:48-50 of the reference); times `scale` where a model has one
+// (on the float32 stream, so that a tied head still reads the table as stored).
 class TokenEmbedding : public Embedding {
 public:
-    explicit TokenEmbedding(const PartSpec& s) : Embedding(s), vocab_(s.get_int("vocab_size")), width_(s.get_int("width")) {}
+    explicit TokenEmbedding(const PartSpec& s)
+        : Embedding(s), vocab_(s.get_int("vocab_size")), width_(s.get_int("width")), scale_((float)s.get_double("scale", 1.0)) {}
     TensorRequests requests() const override {
         TensorRequest w;
         w.shape = {vocab_, width_};
@@ -198,20 +206,26 @@ public:
     void forward(StepContext& ctx, Tensor& x) override {
         const Tensor* pos = ctx.position ? ctx.position->table() : nullptr;
         ops::embed_positions(ctx.launch, ctx.token_ids, ctx.positions, weight_.view, pos, x, ctx.n_tokens);
+        if (scale_ != 1.0f) ops::scale(ctx.launch, x, scale_);
     }
 private:
     int64_t vocab_, width_;
+    float scale_;
     DeviceWeight weight_;
 };
 
-// Output head: logits = y @ W^T in float32, times `logit_scale` where a model has one.  With `tied` the token table itself is the weight: the
+// Output head: logits = y @ W^T in float32, times `logit_scale` where a model has one, then pressed into
+// (-logit_softcap, logit_softcap) by cap * tanh(logit / cap) where a model has that.  With `tied` the token table itself is the weight: the
 // reference ties by naming `wte.weight` twice (:57, a transposed-operand matmul,
 // src/ir/MidIRPass.cpp:30-69), and no second copy exists here either.
 class OutputHead : public Head {
 public:
     explicit OutputHead(const PartSpec& s)
         : Head(s), vocab_(s.get_int("vocab_size")), width_(s.get_int("width")), tied_(s.get_bool("tied", false)),
-          logit_scale_((float)s.get_double("logit_scale", 1.0)), linear_(width_, vocab_, false, "out_in", "head") {}
+          logit_scale_((float)s.get_double("logit_scale", 1.0)), logit_softcap_((float)s.get_double("logit_softcap", 0.0)),
+          linear_(width_, vocab_, false, "out_in", "head") {
+        if (logit_softcap_ < 0.0f) throw ConfigError("output_head: logit_softcap must not be negative");
+    }
     TensorRequests requests() const override {
         if (tied_) return {};
         TensorRequest w;
@@ -233,11 +247,12 @@ public:
     void forward(StepContext& ctx, const Tensor& y, Tensor& logits) override {
         linear_.run(ctx, nullptr, &y, logits, ops::Act::None, nullptr);
         if (logit_scale_ != 1.0f) ops::scale(ctx.launch, logits, logit_scale_);      // on the float32 logits
+        if (logit_softcap_ > 0.0f) ops::softcap(ctx.launch, logits, logit_softcap_);
     }
 private:
     int64_t vocab_, width_;
     bool tied_;
-    float logit_scale_;
+    float logit_scale_, logit_softcap_;
     Linear linear_;
 };
 
@@ -322,7 +337,7 @@ private:
 // Dense feed-forward (kind "dense_mlp"): u = h @ W_up + b_up;  g = act(u);  x += g @ W_down + b_down
 // (src/models/gpt2_small.sandy.go:25-32,40-42 of the reference).  The activation runs in the
 // up-projection's write-back and the residual sum in the down-projection's, both in 32-bit.
-// Parameters: width, inner, activation ("gelu_new" | "gelu"), bias, weight_layout.
+// Parameters: width, inner, activation ("gelu_new" | "gelu" | "relu_squared"), bias, weight_layout.
 // Tensors: "up.weight", "up.bias", "down.weight", "down.bias".
 class DenseMLP : public FeedForward {
 public:
@@ -361,13 +376,15 @@ private:
 };
 
 // "pre_norm": x += mixer(norm_1(x)); x += feed_forward(norm_2(x))
-// (src/models/gpt2_small.sandy.go:34-45 of the reference).  Norm names: "mixer", "feed_forward".
+// (src/models/gpt2_small.sandy.go:34-45 of the reference).  Norm names: "mixer", and "feed_forward" where the
+// layer has a feed-forward.
 class PreNormBlock : public Block {
 public:
     using Block::Block;
     void forward(StepContext& ctx, Tensor& x, const LayerCall& call) override {
         NormedInput h1(ctx, *norms_.at("mixer"), x);
         mixer_->forward(ctx, h1, x, call);
+        if (ff_->empty()) return;
         NormedInput h2(ctx, *norms_.at("feed_forward"), x);
         ff_->forward(ctx, h2, x);
     }
@@ -395,7 +412,7 @@ Table& table() {
         t["mixer"]["causal_attention"] = simple<CausalSelfAttention>();
         t["feed_forward"]["dense_mlp"] = simple<DenseMLP>();
         PartFactory pre;
-        pre.norm_names = {"mixer", "feed_forward"};
+        pre.norm_names = {"mixer"};
         pre.make_block = [](BlockParts p) {
             return std::unique_ptr<Block>(new PreNormBlock(std::move(p.mixer), std::move(p.feed_forward), std::move(p.norms), p.width));
         };
@@ -409,6 +426,7 @@ Table& table() {
         std::call_once(more, [] {
             register_hybrid_parts();
             register_latent_parts();
+            register_capped_parts();
         });
         entered = false;
     }

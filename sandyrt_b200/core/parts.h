@@ -91,6 +91,8 @@ protected:
 };
 
 struct LayerNormParams { Tensor gamma; const Tensor* beta = nullptr; float eps = 0.0f; };
+// An RMS norm's float32 input rows, gain (or null) and eps, for a consumer whose kernel runs the norm itself.
+struct RmsNormParams { Tensor x; const Tensor* gain = nullptr; float eps = 0.0f; };
 
 class Norm : public Part {
 public:
@@ -98,6 +100,8 @@ public:
     virtual void forward(StepContext& ctx, const Tensor& x, Tensor& out, const int* rows, int n_rows) = 0;
     // Kernels that can run a LayerNorm inside themselves ask for its parameters here.
     virtual bool layernorm_params(LayerNormParams& out) const { (void)out; return false; }
+    // ... and kernels that run an RMS norm inside themselves (a token shift behind the norm) here; `x` is left alone.
+    virtual bool rms_params(RmsNormParams& out) const { (void)out; return false; }
     // x += mult * norm(y), both float32: a norm behind a sublayer.  Norms that cannot do this in 32-bit refuse.
     virtual void forward_add(StepContext& ctx, const Tensor& y, float mult, Tensor& x) {
         (void)ctx; (void)y; (void)mult; (void)x;
@@ -140,6 +144,7 @@ public:
     int64_t cols() const { return x_.cols; }
     const Tensor& tensor();                            // computed once and shared
     bool fusable(ops::FusedNorm& out) const;           // the norm's parameters, if it is a LayerNorm
+    bool rms(RmsNormParams& out) const;                // the stream's rows and the norm's parameters, if it is an RMS norm
 private:
     StepContext& ctx_;
     Norm& norm_;
@@ -236,6 +241,9 @@ std::vector<std::string> part_kinds(const std::string& family);
 // Kinds of parts_hybrid.cpp: RMS norm, gated feed-forward, norms on both sides of a sublayer, attention with a sink
 // beside a matrix memory, the gated delta rule, the re-entry mix of a looped span.  Called once by the registry.
 void register_hybrid_parts();
+// Kinds of parts_capped.cpp: attention with normed queries, keys and values, a temperature per head, capped scores and
+// chunks of positions, behind a token shift; the stream's re-entry into a looped span by addition.
+void register_capped_parts();
 // Kinds of parts_latent.cpp: attention over a latent of keys and values, a routed mixture of experts, a factor per
 // channel behind a sublayer, the block whose two sublayers read one normed input.
 void register_latent_parts();

@@ -129,6 +129,11 @@ public:
     void forward_add(StepContext& ctx, const Tensor& y, float mult, Tensor& x) override {
         ops::rmsnorm_add(ctx.launch, y, &gain_.view, eps_, mult, x);
     }
+    bool rms_params(RmsNormParams& p) const override {
+        p.gain = &gain_.view;
+        p.eps = eps_;
+        return true;
+    }
 private:
     int64_t width_;
     float eps_;

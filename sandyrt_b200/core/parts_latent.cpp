@@ -148,10 +148,20 @@ private:
 };
 
 // ---- a routed mixture of experts ------------------------------------------------------------------------------------
-// Parameters: width, inner (an expert's), n_experts, top, activation ("relu_squared"), router_bias.
-// Tensors: "router" [n_experts, width], "router_bias" [n_experts], "up.<k>" [inner, width], "down.<k>" [width, inner].
-// x (+)= sum over a token's chosen experts of weight * down_k(act(up_k h)).  Router logits are a product written in
-// 32-bit plus a 32-bit bias; the routing lives on the device, so a recorded step serves every routing.
+// Parameters: width, inner (an expert's), n_experts, top,
+//   activation   "relu_squared": an expert is down(relu(up h)^2);
+//                "clamped_glu":  g = min(gate h, limit), u = clamp(up h, -limit, limit), down(g sigmoid(glu_alpha g) (u + 1))
+//                (parameters limit, glu_alpha)
+//   scoring      "softmax_top": the `top` largest router logits (+ router_bias) are chosen, weighted by the softmax over
+//                the chosen logits alone (parameter router_bias);
+//                "sigmoid": scores s = sigmoid(logit); the choice is by s + correction (parameter correction: whether
+//                the tensor exists) among the experts of the keep_groups best of n_groups equal groups of neighbours (a
+//                group's score: the sum of its group_rank largest choice scores); the weights are the chosen s over their
+//                sum (+ weight_eps), times weight_scale.
+// Tensors: "router" [n_experts, width], "router_bias" / "correction" [n_experts], "up.<k>" [inner, width], "gate.<k>"
+// likewise (clamped_glu), "down.<k>" [width, inner].
+// x (+)= sum over a token's chosen experts of weight * expert_k(h).  Router logits are a product written in 32-bit;
+// the routing lives on the device, so a recorded step serves every routing.
 class RoutedExperts : public FeedForward {
 public:
     explicit RoutedExperts(const PartSpec& s)
@@ -159,14 +169,37 @@ public:
           top_((int)s.get_int("top")), has_bias_(s.get_bool("router_bias", false)), router_(width_, E_, false, "out_in", "router") {
         if (E_ < 1 || E_ > 2048 || top_ < 1 || top_ > E_) throw ConfigError("routed_experts: n_experts must be 1 .. 2048 and top 1 .. n_experts");
         const std::string a = s.get_string("activation", "relu_squared");
-        if (a != "relu_squared") throw ConfigError("routed_experts: unknown activation '" + a + "'");
+        if (a == "clamped_glu") {
+            glu_ = true;
+            limit_ = (float)s.get_double("limit");
+            alpha_ = (float)s.get_double("glu_alpha", 1.0);
+            if (!(limit_ > 0.0f)) throw ConfigError("routed_experts: limit must be positive");
+        } else if (a != "relu_squared") {
+            throw ConfigError("routed_experts: unknown activation '" + a + "'");
+        }
+        const std::string sc = s.get_string("scoring", "softmax_top");
+        if (sc == "sigmoid") {
+            scored_ = true;
+            has_bias_ = s.get_bool("correction", false);
+            rule_.n_groups = (int)s.get_int("n_groups", 1);
+            rule_.keep_groups = (int)s.get_int("keep_groups", rule_.n_groups);
+            rule_.group_rank = (int)s.get_int("group_rank", 2);
+            rule_.weight_scale = (float)s.get_double("weight_scale", 1.0);
+            rule_.norm_eps = (float)s.get_double("weight_eps", 0.0);
+            if (rule_.n_groups < 1 || E_ % rule_.n_groups || rule_.keep_groups < 1 || rule_.keep_groups > rule_.n_groups ||
+                rule_.group_rank < 1 || top_ > E_ / rule_.n_groups * rule_.keep_groups)
+                throw ConfigError("routed_experts: n_groups must divide n_experts, 1 <= keep_groups <= n_groups, and the kept groups must hold top experts");
+        } else if (sc != "softmax_top") {
+            throw ConfigError("routed_experts: unknown scoring '" + sc + "'");
+        }
     }
     TensorRequests requests() const override {
         TensorRequests t;
         t["router"] = want({(int64_t)E_, width_});
-        if (has_bias_) t["router_bias"] = want({(int64_t)E_}, "bias");
+        if (has_bias_) t[scored_ ? "correction" : "router_bias"] = want({(int64_t)E_}, "bias");
         for (int e = 0; e < E_; e++) {
             t["up." + std::to_string(e)] = want({inner_, width_});
+            if (glu_) t["gate." + std::to_string(e)] = want({inner_, width_});
             t["down." + std::to_string(e)] = want({width_, inner_});
         }
         return t;
@@ -175,9 +208,10 @@ public:
         TensorMap m;
         m["router.weight"] = t.at("router");
         router_.bind(m, dtype);
-        if (has_bias_) bias_ = to_device(t.at("router_bias"), DType::F32);
+        if (has_bias_) bias_ = to_device(t.at(scored_ ? "correction" : "router_bias"), DType::F32);
         std::vector<const HostTensor*> ups, downs;
         for (int e = 0; e < E_; e++) {
+            if (glu_) ups.push_back(&t.at("gate." + std::to_string(e)));      // an expert's rows: its gate, then its up
             ups.push_back(&t.at("up." + std::to_string(e)));
             downs.push_back(&t.at("down." + std::to_string(e)));
         }
@@ -200,10 +234,17 @@ public:
         r.group_start = (int*)ws.raw("moe_group_start", (size_t)(E_ + 1) * sizeof(int));
         r.entry_of_slot = (int*)ws.raw("moe_entry_of_slot", (size_t)slots * sizeof(int));
         r.slot_of_entry = (int*)ws.raw("moe_slot_of_entry", (size_t)slots * sizeof(int));
-        ops::moe_route(l, logits, has_bias_ ? &bias_.view : nullptr, r);
+        if (scored_) ops::moe_route_scored(l, logits, has_bias_ ? &bias_.view : nullptr, rule_, r);
+        else ops::moe_route(l, logits, has_bias_ ? &bias_.view : nullptr, r);
         Tensor a = ws.get("moe_inner", slots, inner_, ctx.compute_dtype);
         Tensor sorted = ws.get("moe_sorted_rows", slots, width_, ctx.compute_dtype);      // for steps whose products want them
-        ops::expert_product(l, r, h.tensor(), true, up_.view, ops::ExpertAct::ReluSquared, a, &sorted);
+        if (glu_) {
+            Tensor gu = ws.get("moe_gate_up", slots, 2 * inner_, ctx.compute_dtype);
+            ops::expert_product(l, r, h.tensor(), true, up_.view, ops::ExpertAct::None, gu, &sorted);
+            ops::glu_clamped(l, gu.col_range(0, inner_), gu.col_range(inner_, 2 * inner_), limit_, alpha_, a);
+        } else {
+            ops::expert_product(l, r, h.tensor(), true, up_.view, ops::ExpertAct::ReluSquared, a, &sorted);
+        }
         Tensor rows = ws.get("moe_rows", slots, width_, DType::F32);
         ops::expert_product(l, r, a, false, down_.view, ops::ExpertAct::None, rows);
         ops::moe_combine(l, r, rows, x, !ctx.overwrite);
@@ -211,7 +252,9 @@ public:
 private:
     int64_t width_, inner_;
     int E_, top_;
-    bool has_bias_;
+    bool has_bias_, glu_ = false, scored_ = false;
+    float limit_ = 0.0f, alpha_ = 1.0f;
+    ops::ScoredRoute rule_;
     Linear router_;
     DeviceWeight bias_, up_, down_;
 };

@@ -3,6 +3,9 @@
 // Formula, as the reference computes it (src/core/TensorCalc.cpp:1241-1311):
 //   s[j] = (q . k_j) * scale            for  max(0, pos+1-window) <= j <= pos   (window 0: all)
 //   p[j] = exp(s[j] - max s) / sum exp(s - max s);   o = sum_j p[j] * v_j
+// Two rules some layers add: with softcap > 0 a score becomes softcap * tanh(s / softcap) before the softmax; with
+// chunk > 0 a query at position pos sees only keys of its own chunk, j >= pos - pos % chunk (chunks are counted from
+// position 0 of the request, wherever the step's tokens start).
 // with query head h reading key/value head h / (H / Hkv) (:1246).  Scores, the softmax and
 // the weighted sum are carried in 32-bit; the reference's CUDA kernels do the same with an
 // online softmax (src/device/cuda/CudaAttentionKernels.cu:171-243).
@@ -100,8 +103,8 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
                        const int* __restrict__ token_seq, const int* __restrict__ positions,
                        T* __restrict__ out, int ld_out,
                        int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                       float scale, int window, int num_pages, const float* __restrict__ sink,
-                       const float* __restrict__ out_gate, int* __restrict__ status) {
+                       float scale, int window, float softcap, int chunk, int num_pages,
+                       const float* __restrict__ sink, const float* __restrict__ out_gate, int* __restrict__ status) {
     __shared__ float q_smem[WARPS_PER_BLOCK][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long pair = (long long)blockIdx.x * WARPS_PER_BLOCK + warp;
@@ -110,7 +113,8 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
     const int s = token_seq[t];
     const int pos = positions[t];
     const int kvh = h / (n_heads / n_kv_heads);
-    const int lo = window > 0 ? max(0, pos + 1 - window) : 0;
+    int lo = window > 0 ? max(0, pos + 1 - window) : 0;
+    if (chunk > 0) lo = max(lo, pos - pos % chunk);
     const int* table = block_table + (size_t)s * max_blocks;
     const long long rows_per_page = page_stride / head_dim;  // page stride in rows of D
 
@@ -136,6 +140,7 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
             } else {
                 row = (long long)page * rows_per_page + (long long)kvh * page_size + (j % page_size);
                 sc = dot_row<T>(k_cache + row * head_dim, qs, head_dim) * scale;
+                if (softcap > 0.0f) sc = softcap * tanhf(sc / softcap);
             }
         }
         const float m_new = fmaxf(m, warp_max(sc));
@@ -199,30 +204,43 @@ SANDY_API int sandy_kv_append(const void* k_src, const void* v_src, int ld_src,
 // q: [n_tokens, H*D] with row stride ld_q; out: [n_tokens, H*D] with row stride ld_out.
 // window 0 = every earlier key is visible.  sink: float32 [H] or null: exp(sink[h]) joins the softmax's
 // denominator.  out_gate: float32 [n_tokens, H] or null: a factor on each head's output.
-SANDY_API int sandy_paged_attention_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+// out_gate: float32 [n_tokens, H] or null: a factor on each head's output.  softcap 0: scores as they are; chunk 0: no chunks.
+SANDY_API int sandy_paged_attention_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache,
                                         long long page_stride, const int* block_table, int max_blocks,
                                         const int* token_seq, const int* positions, void* out, int ld_out,
                                         int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                        float scale, int window, int num_pages, int dtype, const float* sink,
-                                        const float* out_gate, int* status, cudaStream_t stream) {
+                                        float scale, int window, float softcap, int chunk, int num_pages, int dtype,
+                                        const float* sink, const float* out_gate, int* status, cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out)
         return SANDY_ERR_ARGUMENT;
     if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > WIDE_HEAD_DIM) return SANDY_ERR_UNSUPPORTED;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || page_size <= 0 || window < 0) return SANDY_ERR_UNSUPPORTED;
-    if (page_stride % head_dim != 0) return SANDY_ERR_UNSUPPORTED;
+    if (page_stride % head_dim != 0 || softcap < 0.0f || chunk < 0) return SANDY_ERR_UNSUPPORTED;
     const long long pairs = (long long)n_tokens * n_heads;
     const unsigned blocks = (unsigned)((pairs + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
 #define LAUNCH(T)                                                                                     \
     (head_dim <= MAX_HEAD_DIM ? paged_attention_kernel<T, MAX_HEAD_DIM> : paged_attention_kernel<T, WIDE_HEAD_DIM>)<<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>( \
         (const T*)q, ld_q, (const T*)k_cache, (const T*)v_cache, page_stride, block_table, max_blocks, \
         token_seq, positions, (T*)out, ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size,    \
-        scale, window, num_pages, sink, out_gate, status)
+        scale, window, softcap, chunk, num_pages, sink, out_gate, status)
     if (dtype == SANDY_F32) LAUNCH(float);
     else if (dtype == SANDY_BF16) LAUNCH(bf16);
     else return SANDY_ERR_UNSUPPORTED;
 #undef LAUNCH
     return sandy_launch_status();
+}
+
+// The same with plain scores and no chunks.
+SANDY_API int sandy_paged_attention_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                        long long page_stride, const int* block_table, int max_blocks,
+                                        const int* token_seq, const int* positions, void* out, int ld_out,
+                                        int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                        float scale, int window, int num_pages, int dtype, const float* sink,
+                                        const float* out_gate, int* status, cudaStream_t stream) {
+    return sandy_paged_attention_cap(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq, positions,
+                                     out, ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size, scale, window, 0.0f, 0,
+                                     num_pages, dtype, sink, out_gate, status, stream);
 }
 
 // The same without a sink or an output gate.

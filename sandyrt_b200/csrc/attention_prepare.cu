@@ -9,6 +9,9 @@
 //   3. keys and values written into the request's pages, queries into a dense matrix, each head padded
 //      with zeros from its own size up to the cache's head size (key size and value size may differ: the
 //      cache and the attention kernels see one head size, the larger of the two rounded up to 16);
+//      optionally each query head times a number of its own (a learned temperature: it reaches the scores through
+//      the query), and each value head divided by its root mean square over its own entries (eps inside the root,
+//      no gain), in 32-bit, so that the cache holds unit-RMS values;
 //   4. optional per-head output gate: gate_out[t, h] = sigmoid(gate_in[t, h]) * gate_scale, 32-bit, which
 //      the attention kernels multiply into a head's output.
 //
@@ -28,9 +31,11 @@ attention_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
                          const int* __restrict__ block_table, int max_blocks, T* __restrict__ k_cache,
                          T* __restrict__ v_cache, long long page_stride, int page_size, int num_pages, int write_cache,
                          T* __restrict__ q_out, int ld_q, const float* __restrict__ gate_in, int ld_gate,
-                         float* __restrict__ gate_out, float gate_scale, int* __restrict__ status) {
+                         float* __restrict__ gate_out, float gate_scale, const float* __restrict__ q_head_scale,
+                         float v_unit_eps, int* __restrict__ status) {
     __shared__ float scratch[32];
-    extern __shared__ float cs[];                    // cos [rot_dims / 2], sin [rot_dims / 2]
+    extern __shared__ float cs[];                    // cos [rot_dims / 2], sin [rot_dims / 2], then 1 / rms of each value head
+    float* v_inv = cs + rot_dims;
     const int t = blockIdx.x;
     const int half = rot_dims / 2;
     const int pos = positions[t];                    // the step's index arrays were staged before the step
@@ -63,7 +68,17 @@ attention_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
         }
         k_inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)nk + eps);
     }
-    __syncthreads();                                 // cs is complete (block_sum may not have run)
+    if (v_unit_eps > 0.0f)                           // a warp a value head
+        for (int g = threadIdx.x >> 5; g < n_kv_heads; g += blockDim.x >> 5) {
+            float ss = 0.0f;
+            for (int i = threadIdx.x & 31; i < v_dim; i += 32) {
+                const float x = to_f32(row[v_off + g * v_dim + i]);
+                ss = fmaf(x, x, ss);
+            }
+            ss = warp_sum(ss);
+            if ((threadIdx.x & 31) == 0) v_inv[g] = 1.0f / sqrtf(ss / (float)v_dim + v_unit_eps);
+        }
+    __syncthreads();                                 // cs and v_inv are complete (block_sum may not have run)
 
     // where this token's key and value go
     long long page_base = -1;
@@ -88,14 +103,16 @@ attention_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
 
     for (int idx = threadIdx.x; idx < n_heads * pad_dim; idx += blockDim.x) {
         const int h = idx / pad_dim, i = idx % pad_dim;
-        q_out[(size_t)t * ld_q + idx] = from_f32<T>(i < qk_dim ? turned(q_off, q_gain, q_inv, h, i) : 0.0f);
+        q_out[(size_t)t * ld_q + idx] =
+            from_f32<T>(i < qk_dim ? turned(q_off, q_gain, q_inv, h, i) * (q_head_scale ? q_head_scale[h] : 1.0f) : 0.0f);
     }
     if (page_base >= 0) {
         for (int idx = threadIdx.x; idx < n_kv_heads * pad_dim; idx += blockDim.x) {
             const int g = idx / pad_dim, i = idx % pad_dim;
             const long long dst = page_base + (long long)g * page_size * pad_dim + i;
             k_cache[dst] = from_f32<T>(i < qk_dim ? turned(k_off, k_gain, k_inv, g, i) : 0.0f);
-            v_cache[dst] = i < v_dim ? row[v_off + g * v_dim + i] : from_f32<T>(0.0f);
+            if (v_unit_eps > 0.0f) v_cache[dst] = from_f32<T>(i < v_dim ? to_f32(row[v_off + g * v_dim + i]) * v_inv[g] : 0.0f);
+            else v_cache[dst] = i < v_dim ? row[v_off + g * v_dim + i] : from_f32<T>(0.0f);
         }
     }
     (void)nv;
@@ -110,6 +127,38 @@ attention_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
 // k_off (n_kv_heads * qk_dim), values at v_off (n_kv_heads * v_dim).  q_gain / k_gain: float32 or null (no norm).
 // freq: float32 [rot_dims / 2] or null (no rotation).  The cache's head size is pad_dim >= max(qk_dim, v_dim).
 // q_out: [n_tokens, n_heads * pad_dim] of dtype.  gate_in: float32 [n_tokens, >= n_heads] with pitch ld_gate, or null.
+// q_head_scale: float32 [n_heads] or null; v_unit_eps > 0: value heads are divided by their root mean square.
+SANDY_API int sandy_attention_prepare_ext(const void* proj, int ld, int q_off, int k_off, int v_off, int n_tokens, int n_heads,
+                                      int n_kv_heads, int qk_dim, int v_dim, int pad_dim, const float* q_gain,
+                                      const float* k_gain, float eps, const float* freq, int rot_dims, const int* positions,
+                                      const int* token_seq, const int* block_table, int max_blocks, void* k_cache,
+                                      void* v_cache, long long page_stride, int page_size, int num_pages, int write_cache,
+                                      void* q_out, int ld_q, const float* gate_in, int ld_gate, float* gate_out,
+                                      float gate_scale, const float* q_head_scale, float v_unit_eps, int dtype, int* status,
+                                      cudaStream_t stream) {
+    if (n_tokens == 0) return SANDY_OK;
+    if (!proj || !positions || !token_seq || !q_out || (write_cache && (!block_table || !k_cache || !v_cache)))
+        return SANDY_ERR_ARGUMENT;
+    if (pad_dim < qk_dim || pad_dim < v_dim || rot_dims < 0 || rot_dims > qk_dim || (rot_dims & 1) || (gate_out && !gate_in))
+        return SANDY_ERR_UNSUPPORTED;
+    const size_t smem = ((size_t)rot_dims + (size_t)n_kv_heads) * sizeof(float);
+    if (smem > 32 * 1024) return SANDY_ERR_UNSUPPORTED;
+    if (dtype == SANDY_F32)
+        return sandy_launch(attention_prepare_kernel<float>, dim3(n_tokens), dim3(THREADS), smem, stream, (const float*)proj,
+                            ld, q_off, k_off, v_off, n_heads, n_kv_heads, qk_dim, v_dim, pad_dim, q_gain, k_gain, eps, freq,
+                            rot_dims, positions, token_seq, block_table, max_blocks, (float*)k_cache, (float*)v_cache,
+                            page_stride, page_size, num_pages, write_cache, (float*)q_out, ld_q, gate_in, ld_gate, gate_out,
+                            gate_scale, q_head_scale, v_unit_eps, status);
+    if (dtype == SANDY_BF16)
+        return sandy_launch(attention_prepare_kernel<bf16>, dim3(n_tokens), dim3(THREADS), smem, stream, (const bf16*)proj,
+                            ld, q_off, k_off, v_off, n_heads, n_kv_heads, qk_dim, v_dim, pad_dim, q_gain, k_gain, eps, freq,
+                            rot_dims, positions, token_seq, block_table, max_blocks, (bf16*)k_cache, (bf16*)v_cache,
+                            page_stride, page_size, num_pages, write_cache, (bf16*)q_out, ld_q, gate_in, ld_gate, gate_out,
+                            gate_scale, q_head_scale, v_unit_eps, status);
+    return SANDY_ERR_UNSUPPORTED;
+}
+
+// The same without a factor per query head and with the values as projected.
 SANDY_API int sandy_attention_prepare(const void* proj, int ld, int q_off, int k_off, int v_off, int n_tokens, int n_heads,
                                       int n_kv_heads, int qk_dim, int v_dim, int pad_dim, const float* q_gain,
                                       const float* k_gain, float eps, const float* freq, int rot_dims, const int* positions,
@@ -117,24 +166,8 @@ SANDY_API int sandy_attention_prepare(const void* proj, int ld, int q_off, int k
                                       void* v_cache, long long page_stride, int page_size, int num_pages, int write_cache,
                                       void* q_out, int ld_q, const float* gate_in, int ld_gate, float* gate_out,
                                       float gate_scale, int dtype, int* status, cudaStream_t stream) {
-    if (n_tokens == 0) return SANDY_OK;
-    if (!proj || !positions || !token_seq || !q_out || (write_cache && (!block_table || !k_cache || !v_cache)))
-        return SANDY_ERR_ARGUMENT;
-    if (pad_dim < qk_dim || pad_dim < v_dim || rot_dims < 0 || rot_dims > qk_dim || (rot_dims & 1) || (gate_out && !gate_in))
-        return SANDY_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)rot_dims * sizeof(float);
-    if (smem > 32 * 1024) return SANDY_ERR_UNSUPPORTED;
-    if (dtype == SANDY_F32)
-        return sandy_launch(attention_prepare_kernel<float>, dim3(n_tokens), dim3(THREADS), smem, stream, (const float*)proj,
-                            ld, q_off, k_off, v_off, n_heads, n_kv_heads, qk_dim, v_dim, pad_dim, q_gain, k_gain, eps, freq,
-                            rot_dims, positions, token_seq, block_table, max_blocks, (float*)k_cache, (float*)v_cache,
-                            page_stride, page_size, num_pages, write_cache, (float*)q_out, ld_q, gate_in, ld_gate, gate_out,
-                            gate_scale, status);
-    if (dtype == SANDY_BF16)
-        return sandy_launch(attention_prepare_kernel<bf16>, dim3(n_tokens), dim3(THREADS), smem, stream, (const bf16*)proj,
-                            ld, q_off, k_off, v_off, n_heads, n_kv_heads, qk_dim, v_dim, pad_dim, q_gain, k_gain, eps, freq,
-                            rot_dims, positions, token_seq, block_table, max_blocks, (bf16*)k_cache, (bf16*)v_cache,
-                            page_stride, page_size, num_pages, write_cache, (bf16*)q_out, ld_q, gate_in, ld_gate, gate_out,
-                            gate_scale, status);
-    return SANDY_ERR_UNSUPPORTED;
+    return sandy_attention_prepare_ext(proj, ld, q_off, k_off, v_off, n_tokens, n_heads, n_kv_heads, qk_dim, v_dim, pad_dim, q_gain,
+                                       k_gain, eps, freq, rot_dims, positions, token_seq, block_table, max_blocks, k_cache, v_cache,
+                                       page_stride, page_size, num_pages, write_cache, q_out, ld_q, gate_in, ld_gate, gate_out,
+                                       gate_scale, nullptr, 0.0f, dtype, status, stream);
 }

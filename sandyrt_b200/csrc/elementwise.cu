@@ -8,6 +8,11 @@
 //   sandy_scale_add   x[t, j] += gain[j] * y[t, j]           a sublayer's result joins the stream through a learned
 //                                                            factor per channel (layer scale); all float32
 //   sandy_scale_f32   x[i] *= s                              float32 logits times a constant
+//   sandy_glu_clamped out[t, j] = g sigmoid(alpha g) (u + 1), g = min(a[t, j], limit), u = clamp(b[t, j], -limit, limit)
+//                                                            a gated inner activation whose two halves are cut off
+//   sandy_stream_add  x[t, j] += x0[t, j] + row[j]            the stream re-entering a looped span: the embedding's
+//                                                            output and one learned vector join it; all float32
+//   sandy_softcap_f32 x[i] = cap tanh(x[i] / cap)            float32 logits pressed into (-cap, cap)
 //
 // The activation is computed in 32-bit and the result rounded once.
 #include "common.cuh"
@@ -61,6 +66,43 @@ scale_add_kernel(const float* __restrict__ y, int ldy, const float* __restrict__
         if (y2) branch += gain2[j] * y2[t * ldy2 + j];
         x[t * ldx + j] += branch;
     }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+glu_clamped_kernel(const T* __restrict__ a, const T* __restrict__ b, int ld_in, T* __restrict__ out, int ld_out, int rows,
+                   int cols, float limit, float alpha) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long n = (long long)rows * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / cols, j = i % cols;
+        const float g = fminf(to_f32(a[t * ld_in + j]), limit);
+        const float u = fminf(fmaxf(to_f32(b[t * ld_in + j]), -limit), limit);
+        out[t * ld_out + j] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+
+__global__ void __launch_bounds__(256)
+stream_add_kernel(float* __restrict__ x, int ldx, const float* __restrict__ x0, int ldx0, const float* __restrict__ row,
+                  int rows, int cols) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long n = (long long)rows * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / cols, j = i % cols;
+        float v = x[t * ldx + j];
+        if (x0) v += x0[t * ldx0 + j];
+        if (row) v += row[j];
+        x[t * ldx + j] = v;
+    }
+}
+
+__global__ void __launch_bounds__(256) softcap_f32_kernel(float* __restrict__ x, long long n, float cap) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] / cap);
 }
 
 __global__ void __launch_bounds__(256) scale_f32_kernel(float* __restrict__ x, long long n, float s) {
@@ -120,4 +162,36 @@ SANDY_API int sandy_scale_f32(float* x, long long n, float s, cudaStream_t strea
     if (n == 0) return SANDY_OK;
     if (!x) return SANDY_ERR_ARGUMENT;
     return sandy_launch(scale_f32_kernel, dim3(blocks_for(n)), dim3(256), 0, stream, x, n, s);
+}
+
+// a, b: [rows, cols] of dtype with the same pitch ld_in; out: [rows, cols] of dtype.  limit > 0.
+SANDY_API int sandy_glu_clamped(const void* a, const void* b, int ld_in, void* out, int ld_out, int rows, int cols, float limit,
+                                float alpha, int dtype, cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return SANDY_OK;
+    if (!a || !b || !out) return SANDY_ERR_ARGUMENT;
+    if (!(limit > 0.0f)) return SANDY_ERR_UNSUPPORTED;
+    const unsigned grid = blocks_for((long long)rows * cols);
+    if (dtype == SANDY_F32)
+        return sandy_launch(glu_clamped_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)a, (const float*)b, ld_in,
+                            (float*)out, ld_out, rows, cols, limit, alpha);
+    if (dtype == SANDY_BF16)
+        return sandy_launch(glu_clamped_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)a, (const bf16*)b, ld_in,
+                            (bf16*)out, ld_out, rows, cols, limit, alpha);
+    return SANDY_ERR_UNSUPPORTED;
+}
+
+// x [rows, cols] += x0 [rows, cols] + row [cols]; x0 and row may each be null; all float32.
+SANDY_API int sandy_stream_add(float* x, int ldx, const float* x0, int ldx0, const float* row, int rows, int cols,
+                               cudaStream_t stream) {
+    if (rows == 0 || cols == 0 || (!x0 && !row)) return SANDY_OK;
+    if (!x) return SANDY_ERR_ARGUMENT;
+    return sandy_launch(stream_add_kernel, dim3(blocks_for((long long)rows * cols)), dim3(256), 0, stream, x, ldx, x0, ldx0, row,
+                        rows, cols);
+}
+
+SANDY_API int sandy_softcap_f32(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n == 0) return SANDY_OK;
+    if (!x) return SANDY_ERR_ARGUMENT;
+    if (!(cap > 0.0f)) return SANDY_ERR_UNSUPPORTED;
+    return sandy_launch(softcap_f32_kernel, dim3(blocks_for(n)), dim3(256), 0, stream, x, n, cap);
 }

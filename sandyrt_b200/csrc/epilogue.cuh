@@ -35,14 +35,22 @@ __device__ __forceinline__ float gelu_tanh_fast(float u) {
     return (0.5f * u) * (1.0f + t);
 }
 
+// relu(u)^2
+__device__ __forceinline__ float relu_squared(float u) {
+    u = fmaxf(u, 0.0f);
+    return u * u;
+}
+
 __device__ __forceinline__ float apply_act_fast(float v, int act) {
     if (act == SANDY_ACT_GELU_TANH) return gelu_tanh_fast(v);
     if (act == SANDY_ACT_GELU_ERF) return gelu_erf(v);
+    if (act == SANDY_ACT_RELU_SQUARED) return relu_squared(v);
     return v;
 }
 
 __device__ __forceinline__ float apply_act(float v, int act) {
     if (act == SANDY_ACT_GELU_TANH) return gelu_tanh(v);
     if (act == SANDY_ACT_GELU_ERF) return gelu_erf(v);
+    if (act == SANDY_ACT_RELU_SQUARED) return relu_squared(v);
     return v;
 }

@@ -93,6 +93,7 @@ __device__ __forceinline__ void finish(float acc, int m, int n, float bias, cons
     float v = acc + bias;
     if (ACT == SANDY_ACT_GELU_TANH) v = gelu_tanh_fast(v);
     if (ACT == SANDY_ACT_GELU_ERF) v = gelu_erf(v);
+    if (ACT == SANDY_ACT_RELU_SQUARED) v = relu_squared(v);
     if (KV) {
         if (n >= f.q_cols) {
             const int page = kv_page[m];
@@ -143,6 +144,9 @@ __device__ __forceinline__ void finish_dispatch(int m0, int step, int count, int
     } else if (f.act == SANDY_ACT_GELU_ERF) {
         if (f.out_f32) SANDY_FINISH(SANDY_ACT_GELU_ERF, false, false, true);
         else SANDY_FINISH(SANDY_ACT_GELU_ERF, false, false, false);
+    } else if (f.act == SANDY_ACT_RELU_SQUARED) {
+        if (f.out_f32) SANDY_FINISH(SANDY_ACT_RELU_SQUARED, false, false, true);
+        else SANDY_FINISH(SANDY_ACT_RELU_SQUARED, false, false, false);
     } else {
         if (f.out_f32) SANDY_FINISH(SANDY_ACT_NONE, false, false, true);
         else SANDY_FINISH(SANDY_ACT_NONE, false, false, false);

@@ -3,6 +3,12 @@
 //   sandy_moe_route    per token: logits z = router product + bias (32-bit); the `top` largest (ties: the lower
 //                      expert first) are chosen, their weights are the softmax over the chosen logits alone.
 //                      Entry t * top + j holds the j-th choice of token t.
+//   sandy_moe_route_scored
+//                      per token: scores s = sigmoid(z); choice scores c = s + correction; the experts form `n_groups`
+//                      equal groups of neighbours, a group's score is the sum of its `group_rank` largest choice
+//                      scores, and only experts of the `keep_groups` best groups can be chosen (ties: the lower group
+//                      and the lower expert first); the `top` largest c among those are chosen; their weights are
+//                      their s over the sum of the chosen s (+ norm_eps), times weight_scale.
 //   sandy_moe_group    entries sorted by expert: group_start[e] .. group_start[e+1]-1 are expert e's slots;
 //                      entry_of_slot and slot_of_entry are the two directions of the permutation.  Which slot of
 //                      its expert an entry gets is not fixed from run to run; nothing depends on it, since every
@@ -52,6 +58,83 @@ moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restri
         __syncwarp();
     }
     for (int j = lane; j < top; j += 32) weight_of[(size_t)t * top + j] /= sum;      // lane 0's writes are visible after the syncwarp
+}
+
+// A warp a token.  Shared memory per warp: choice scores [n_experts], plain scores [n_experts], group scores [n_groups].
+__global__ void __launch_bounds__(128)
+moe_route_scored_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction, int n_tokens,
+                        int n_experts, int top, int n_groups, int keep_groups, int group_rank, float weight_scale,
+                        float norm_eps, int* __restrict__ expert_of, float* __restrict__ weight_of) {
+    extern __shared__ float route_smem[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= n_tokens) return;
+    float* c = route_smem + (size_t)warp * (2 * n_experts + n_groups);
+    float* sc = c + n_experts;
+    float* gs = sc + n_experts;
+    for (int e = lane; e < n_experts; e += 32) {
+        const float s = 1.0f / (1.0f + expf(-logits[(size_t)t * ld + e]));
+        sc[e] = s;
+        c[e] = s + (correction ? correction[e] : 0.0f);
+    }
+    __syncwarp();
+    if (n_groups > 1 && keep_groups < n_groups) {
+        const int per = n_experts / n_groups;
+        // a lane a group: the sum of its group_rank largest choice scores
+        for (int g = lane; g < n_groups; g += 32) {
+            float sum = 0.0f;
+            for (int i = 0; i < per; i++) {          // an entry counts if fewer than group_rank entries are ahead of it
+                const float v = c[g * per + i];
+                int ahead = 0;
+                for (int k = 0; k < per; k++) {
+                    const float o = c[g * per + k];
+                    if (o > v || (o == v && k < i)) ahead++;
+                }
+                if (ahead < group_rank) sum += v;
+            }
+            gs[g] = sum;
+        }
+        __syncwarp();
+        // a lane a group again: a group is kept if fewer than keep_groups groups are ahead of it
+        for (int g = lane; g < n_groups; g += 32) {
+            int ahead = 0;
+            const float v = gs[g];
+            for (int k = 0; k < n_groups; k++) {
+                const float o = gs[k];
+                if (o > v || (o == v && k < g)) ahead++;
+            }
+            if (ahead >= keep_groups)
+                for (int i = 0; i < per; i++) c[g * per + i] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    float sum = 0.0f;
+    for (int j = 0; j < top; j++) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = c[e];
+            if (v > best) { best = v; arg = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg == 0x7fffffff) arg = j;              // nothing left to choose from (NaN logits): any expert
+        const float w = sc[arg];
+        sum += w;
+        if (lane == 0) {
+            expert_of[(size_t)t * top + j] = arg;
+            weight_of[(size_t)t * top + j] = w;
+            c[arg] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    for (int j = lane; j < top; j += 32) weight_of[(size_t)t * top + j] = weight_of[(size_t)t * top + j] / (sum + norm_eps) * weight_scale;
 }
 
 __global__ void __launch_bounds__(1024)
@@ -129,6 +212,22 @@ SANDY_API int sandy_moe_route(const float* logits, int ld, const float* bias, in
     return sandy_launch(moe_route_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps),
                         (size_t)warps * n_experts * sizeof(float), stream, logits, ld, bias, n_tokens, n_experts, top, expert_of,
                         weight_of);
+}
+
+// logits: float32 [n_tokens, >= n_experts] with pitch ld; correction float32 [n_experts] or null; n_groups divides
+// n_experts; 1 <= keep_groups <= n_groups; with n_groups 1 (or every group kept) the groups play no part.
+SANDY_API int sandy_moe_route_scored(const float* logits, int ld, const float* correction, int n_tokens, int n_experts, int top,
+                                     int n_groups, int keep_groups, int group_rank, float weight_scale, float norm_eps,
+                                     int* expert_of, float* weight_of, cudaStream_t stream) {
+    if (n_tokens == 0) return SANDY_OK;
+    if (!logits || !expert_of || !weight_of) return SANDY_ERR_ARGUMENT;
+    if (top < 1 || top > n_experts || n_experts > 2048 || n_groups < 1 || n_experts % n_groups || keep_groups < 1 ||
+        keep_groups > n_groups || group_rank < 1 || top > (n_experts / n_groups) * keep_groups)
+        return SANDY_ERR_UNSUPPORTED;
+    const int warps = 4;
+    return sandy_launch(moe_route_scored_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps),
+                        (size_t)warps * (2 * n_experts + n_groups) * sizeof(float), stream, logits, ld, correction, n_tokens,
+                        n_experts, top, n_groups, keep_groups, group_rank, weight_scale, norm_eps, expert_of, weight_of);
 }
 
 SANDY_API int sandy_moe_group(const int* expert_of, int n_entries, int n_experts, int* group_start, int* entry_of_slot,

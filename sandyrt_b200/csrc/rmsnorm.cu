@@ -9,6 +9,14 @@
 //                                                                                    mixer: a norm per head, then
 //                                                                                    an output gate)
 //
+//   sandy_rmsnorm_shift  h[t] = norm(x[t]) * gain;  out[t] = h[t] + (h[t-1] - h[t]) * mix                (token shift: what a
+//                                                                                    mixer reads leans towards the
+//                                                                                    token before; the h before a
+//                                                                                    request's first token of the
+//                                                                                    step is its state row, zeros at
+//                                                                                    its very first token)
+//   sandy_rmsnorm_keep   state[slot of s] = norm(x[last token of s]) * gain          for requests with several tokens
+//
 // The mean is over the row (or the head) with eps inside the root.  The input is float32 (the residual
 // stream, a branch, a recurrence's read-out), the gain float32 or absent, sums are float32; only the
 // result is rounded, once, to the output's type.
@@ -101,6 +109,62 @@ int launch(const float* x, int ldx, const float* gain, TO* out, int ldo, const i
 #undef CASE
     return sandy_launch(rmsnorm_wide_kernel<TO, MODE>, dim3(n_rows), dim3(256), 0, stream, x, ldx, gain, out, ldo, rows,
                         width, eps, mult);
+}
+
+// Token shift behind the norm, a block per token.  h of the token before is recomputed from its row of the stream
+// (same sums in the same order as that token's own block forms them), or read from the request's state row for the
+// first token of the request in this step.  A request with ONE token in the step also writes its h into the state
+// here: its block is the row's only reader and writer.  Requests with more tokens leave that to keep_last_kernel,
+// which runs behind this one, so that no block writes a row another block of the same launch reads.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_shift_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ gain, const float* __restrict__ mix,
+                     float* __restrict__ state, long long state_stride, const int* __restrict__ token_seq,
+                     const int* __restrict__ q_start, const int* __restrict__ seq_slots, TO* __restrict__ out, int ldo,
+                     int width, float eps) {
+    __shared__ float scratch[32], scratch_prev[32];
+    const int t = blockIdx.x;
+    const int s = token_seq[t];                      // the step's index arrays were staged before the step
+    const int first = q_start[s], last = q_start[s + 1] - 1;
+    float* srow = state + (long long)seq_slots[s] * state_stride;
+    pdl_wait();
+    pdl_launch_dependents();
+    const float* row = x + (size_t)t * ldx;
+    const float* prow = x + (size_t)(t > first ? t - 1 : t) * ldx;
+    float ss = 0.0f, sp = 0.0f;
+    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+        ss = fmaf(row[e], row[e], ss);
+        sp = fmaf(prow[e], prow[e], sp);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+    const float inv_prev = 1.0f / sqrtf(block_sum(sp, scratch_prev) / (float)width + eps);
+    TO* orow = out + (size_t)t * ldo;
+    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+        const float g = gain ? gain[e] : 1.0f;
+        const float h = row[e] * inv * g;
+        const float before = t > first ? prow[e] * inv_prev * g : srow[e];
+        orow[e] = from_f32<TO>(h + (before - h) * mix[e]);
+        if (first == last) srow[e] = h;
+    }
+}
+
+// A block per request of the step; requests with one token were served by the kernel above.
+__global__ void __launch_bounds__(256)
+keep_last_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ gain, float* __restrict__ state,
+                 long long state_stride, const int* __restrict__ q_start, const int* __restrict__ seq_slots, int width,
+                 float eps) {
+    __shared__ float scratch[32];
+    const int s = blockIdx.x;
+    const int first = q_start[s], last = q_start[s + 1] - 1;
+    pdl_wait();
+    pdl_launch_dependents();
+    if (last <= first) return;
+    const float* row = x + (size_t)last * ldx;
+    float ss = 0.0f;
+    for (int e = threadIdx.x; e < width; e += blockDim.x) ss = fmaf(row[e], row[e], ss);
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+    float* srow = state + (long long)seq_slots[s] * state_stride;
+    for (int e = threadIdx.x; e < width; e += blockDim.x) srow[e] = row[e] * inv * (gain ? gain[e] : 1.0f);
 }
 
 // One warp per (token, head).  gain_stride: 0 when all heads share one gain of `dim` entries, `dim` when
@@ -196,4 +260,33 @@ SANDY_API int sandy_head_norm_gate(const float* o, int ldo, const float* gain, i
     CASE(SANDY_F32, SANDY_BF16, float, bf16);
 #undef CASE
     return SANDY_ERR_UNSUPPORTED;
+}
+
+// x: float32 [n_tokens, width] (pitch ldx); gain: float32 [width] or null; mix: float32 [width]; state: float32 rows of
+// `state_stride` floats, one per state slot, the first `width` of which hold the request's last h; out: [n_tokens,
+// width] of out_dtype.  token_seq [n_tokens], q_start [n_seqs + 1], seq_slots [n_seqs]: the step's index arrays.
+SANDY_API int sandy_rmsnorm_shift(const float* x, int ldx, const float* gain, const float* mix, float* state,
+                                  long long state_stride, const int* token_seq, const int* q_start, const int* seq_slots,
+                                  void* out, int ldo, int n_tokens, int width, float eps, int out_dtype, cudaStream_t stream) {
+    if (n_tokens == 0) return SANDY_OK;
+    if (!x || !mix || !state || !token_seq || !q_start || !seq_slots || !out || width <= 0 || state_stride < width)
+        return SANDY_ERR_ARGUMENT;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (out_dtype == SANDY_F32)
+        return sandy_launch(rmsnorm_shift_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, x, ldx, gain, mix, state,
+                            state_stride, token_seq, q_start, seq_slots, (float*)out, ldo, width, eps);
+    if (out_dtype == SANDY_BF16)
+        return sandy_launch(rmsnorm_shift_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, x, ldx, gain, mix, state,
+                            state_stride, token_seq, q_start, seq_slots, (bf16*)out, ldo, width, eps);
+    return SANDY_ERR_UNSUPPORTED;
+}
+
+// Runs behind sandy_rmsnorm_shift in steps that hold a request with more than one token.
+SANDY_API int sandy_rmsnorm_keep(const float* x, int ldx, const float* gain, float* state, long long state_stride,
+                                 const int* q_start, const int* seq_slots, int n_seqs, int width, float eps,
+                                 cudaStream_t stream) {
+    if (n_seqs == 0) return SANDY_OK;
+    if (!x || !state || !q_start || !seq_slots || width <= 0 || state_stride < width) return SANDY_ERR_ARGUMENT;
+    return sandy_launch(keep_last_kernel, dim3(n_seqs), dim3(width >= 1024 ? 256 : 128), 0, stream, x, ldx, gain, state,
+                        state_stride, q_start, seq_slots, width, eps);
 }

@@ -109,6 +109,13 @@ int sandy_paged_attention_ext(const void* q, int ld_q, const void* k_cache, cons
                               int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
                               int window, int num_pages, int dtype, const float* sink, const float* out_gate, int* status,
                               cudaStream_t stream);
+/* ... and with two rules on the scores: softcap > 0 presses a score into softcap * tanh(score / softcap); chunk > 0
+   lets a query see only the keys of its own chunk of positions (j >= pos - pos % chunk).  Zero switches a rule off. */
+int sandy_paged_attention_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                              const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
+                              int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
+                              int window, float softcap, int chunk, int num_pages, int dtype, const float* sink,
+                              const float* out_gate, int* status, cudaStream_t stream);
 int sandy_decode_attention_cluster_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
                                        const int* block_table, int max_blocks, const int* token_seq, const int* positions,
                                        void* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
@@ -156,7 +163,20 @@ int sandy_attention_prepare(const void* proj, int ld, int q_off, int k_off, int 
                             int page_size, int num_pages, int write_cache, void* q_out, int ld_q, const float* gate_in,
                             int ld_gate, float* gate_out, float gate_scale, int dtype, int* status, cudaStream_t stream);
 
+int sandy_attention_prepare_ext(const void* proj, int ld, int q_off, int k_off, int v_off, int n_tokens, int n_heads,
+                                int n_kv_heads, int qk_dim, int v_dim, int pad_dim, const float* q_gain, const float* k_gain,
+                                float eps, const float* freq, int rot_dims, const int* positions, const int* token_seq,
+                                const int* block_table, int max_blocks, void* k_cache, void* v_cache, long long page_stride,
+                                int page_size, int num_pages, int write_cache, void* q_out, int ld_q, const float* gate_in,
+                                int ld_gate, float* gate_out, float gate_scale, const float* q_head_scale, float v_unit_eps,
+                                int dtype, int* status, cudaStream_t stream);
+
 /* rmsnorm.cu */
+int sandy_rmsnorm_shift(const float* x, int ldx, const float* gain, const float* mix, float* state, long long state_stride,
+                        const int* token_seq, const int* q_start, const int* seq_slots, void* out, int ldo, int n_tokens,
+                        int width, float eps, int out_dtype, cudaStream_t stream);
+int sandy_rmsnorm_keep(const float* x, int ldx, const float* gain, float* state, long long state_stride, const int* q_start,
+                       const int* seq_slots, int n_seqs, int width, float eps, cudaStream_t stream);
 int sandy_rmsnorm(const float* x, int ldx, const float* gain, void* out, int ldo, const int* rows, int n_rows, int width,
                   float eps, int out_dtype, cudaStream_t stream);
 int sandy_rmsnorm_add(const float* y, int ldy, const float* gain, float* x, int ldx, int n_rows, int width, float eps,
@@ -172,6 +192,10 @@ int sandy_cast_cols(const float* x, int ldx, void* out, int ld_out, int rows, in
 int sandy_scale_add(const float* y, int ldy, const float* gain, const float* y2, int ldy2, const float* gain2, float* x, int ldx,
                     int rows, int cols, cudaStream_t stream);
 int sandy_scale_f32(float* x, long long n, float s, cudaStream_t stream);
+int sandy_glu_clamped(const void* a, const void* b, int ld_in, void* out, int ld_out, int rows, int cols, float limit,
+                      float alpha, int dtype, cudaStream_t stream);
+int sandy_stream_add(float* x, int ldx, const float* x0, int ldx0, const float* row, int rows, int cols, cudaStream_t stream);
+int sandy_softcap_f32(float* x, long long n, float cap, cudaStream_t stream);
 
 /* latent_prepare.cu */
 int sandy_latent_prepare(const float* down, int ld_down, int n_tokens, int q_rank, int kv_rank, int rot_dim, const float* q_gain,
@@ -194,6 +218,9 @@ int sandy_expert_product_tc(const void* a, int lda, const void* w, int ldw, void
 /* moe.cu */
 int sandy_moe_route(const float* logits, int ld, const float* bias, int n_tokens, int n_experts, int top, int* expert_of,
                     float* weight_of, cudaStream_t stream);
+int sandy_moe_route_scored(const float* logits, int ld, const float* correction, int n_tokens, int n_experts, int top,
+                           int n_groups, int keep_groups, int group_rank, float weight_scale, float norm_eps, int* expert_of,
+                           float* weight_of, cudaStream_t stream);
 int sandy_moe_group(const int* expert_of, int n_entries, int n_experts, int* group_start, int* entry_of_slot, int* slot_of_entry,
                     cudaStream_t stream);
 int sandy_moe_gather(const void* x, long long pitch_x, const int* entry_of_slot, int top, void* out, long long pitch_out, int n_slots,

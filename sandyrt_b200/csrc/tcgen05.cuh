@@ -495,6 +495,9 @@ __device__ __forceinline__ void write_back_warp(uint32_t taddr, uint8_t* tiles, 
     else if (ep.act == SANDY_ACT_GELU_ERF)
         write_back_warp_as<NCHUNKS, NTILES, SANDY_ACT_GELU_ERF, false>(taddr, tiles, row0, col_first, ep, map_out, M, N, kv_page,
                                                                        kv_slot, status, bias, after_loads);
+    else if (ep.act == SANDY_ACT_RELU_SQUARED)
+        write_back_warp_as<NCHUNKS, NTILES, SANDY_ACT_RELU_SQUARED, false>(taddr, tiles, row0, col_first, ep, map_out, M, N, kv_page,
+                                                                           kv_slot, status, bias, after_loads);
     else
         write_back_warp_as<NCHUNKS, NTILES, SANDY_ACT_NONE, false>(taddr, tiles, row0, col_first, ep, map_out, M, N, kv_page, kv_slot,
                                                                    status, bias, after_loads);

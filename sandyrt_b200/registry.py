@@ -41,9 +41,10 @@ def _builtin_config_classes() -> Dict[str, Type[ModelConfig]]:
     from .config.gpt2 import GPT2Config
     from .config.panupel import PanupelConfig
     from .config.sovezen import SovezenConfig
+    from .config.bilurax import BiluraxConfig
 
     return {GPT2Config.architecture: GPT2Config, PanupelConfig.architecture: PanupelConfig,
-            SovezenConfig.architecture: SovezenConfig}
+            SovezenConfig.architecture: SovezenConfig, BiluraxConfig.architecture: BiluraxConfig}
 
 
 def _text(s: str) -> int:
