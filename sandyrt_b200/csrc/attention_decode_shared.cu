@@ -67,9 +67,9 @@ __global__ void __launch_bounds__(WARPS * 32)
 decode_shared_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                      long long page_stride, const int* __restrict__ block_table, int max_blocks,
                      const int* __restrict__ token_seq, const int* __restrict__ positions, bf16* __restrict__ out, int ld_out,
-                     int n_heads, int n_kv_heads, int page_size, float scale, int window, int splits, int num_pages,
-                     const float* __restrict__ sink, const float* __restrict__ out_gate, float* __restrict__ scratch,
-                     int* __restrict__ status) {
+                     int n_heads, int n_kv_heads, int page_size, float scale, int window, float softcap, int chunk, int splits,
+                     int num_pages, const float* __restrict__ sink, const float* __restrict__ out_gate,
+                     float* __restrict__ scratch, int* __restrict__ status) {
     constexpr int PITCH = D + 8;                       // elements: ldmatrix rows fall on different banks
     constexpr int PIECES = D / 8;                      // 16-byte pieces of a key row
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -87,7 +87,8 @@ decode_shared_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __restric
     pdl_launch_dependents();
     const int pos = positions[t];
     const int* table = block_table + (size_t)token_seq[t] * max_blocks;
-    const int lo = window > 0 ? max(0, pos + 1 - window) : 0;
+    int lo = window > 0 ? max(0, pos + 1 - window) : 0;
+    if (chunk > 0) lo = max(lo, pos - pos % chunk);          // a query sees the keys of its own chunk of positions
     const int n_groups = (pos + 1 - lo + GROUP - 1) / GROUP;
     const int per_split = (n_groups + splits - 1) / splits;
     const int g_begin = split * per_split, g_end = min(n_groups, g_begin + per_split);
@@ -133,6 +134,7 @@ decode_shared_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __restric
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
     const float s2 = scale * LOG2E;
+    const float cap2 = softcap * LOG2E, over_cap = softcap > 0.0f ? scale / softcap : 0.0f;      // capped: cap tanh(s scale / cap)
     int g = g_begin + warp, st = 0;
     if (g < g_end) fetch(g, 0);
     for (; g < g_end; g += WARPS, st ^= 1) {
@@ -160,7 +162,8 @@ decode_shared_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __restric
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const int key = key0 + nt * 8 + tq * 2 + (j & 1);
-                s[nt][j] = key <= pos ? s[nt][j] * s2 : -INFINITY;
+                const float sc = softcap > 0.0f ? cap2 * tanhf(s[nt][j] * over_cap) : s[nt][j] * s2;
+                s[nt][j] = key <= pos ? sc : -INFINITY;
             }
         unsigned pa[4];
 #pragma unroll
@@ -295,8 +298,8 @@ size_t smem_bytes(bool one_plane) {
 template <int D>
 int launch(const bf16* q, int ld_q, const bf16* k, const bf16* v, long long page_stride, const int* block_table, int max_blocks,
            const int* token_seq, const int* positions, bf16* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int page_size,
-           float scale, int window, int splits, int num_pages, const float* sink, const float* out_gate, float* scratch, int* status,
-           cudaStream_t stream) {
+           float scale, int window, float softcap, int chunk, int splits, int num_pages, const float* sink, const float* out_gate,
+           float* scratch, int* status, cudaStream_t stream) {
     static bool configured = false;
     const size_t smem = smem_bytes<D>(k == v);
     if (!configured) {
@@ -307,7 +310,8 @@ int launch(const bf16* q, int ld_q, const bf16* k, const bf16* v, long long page
     const int group_heads = n_heads / n_kv_heads, tiles = n_kv_heads * ((group_heads + ROWS - 1) / ROWS);
     int code = sandy_launch(decode_shared_kernel<D>, dim3(splits, tiles, n_tokens), dim3(WARPS * 32), smem, stream, q, ld_q, k, v,
                             page_stride, block_table, max_blocks, token_seq, positions, out, ld_out, n_heads, n_kv_heads, page_size,
-                            scale, window, splits, num_pages, sink, out_gate, splits > 1 ? scratch : (float*)nullptr, status);
+                            scale, window, softcap, chunk, splits, num_pages, sink, out_gate, splits > 1 ? scratch : (float*)nullptr,
+                            status);
     if (code != SANDY_OK || splits == 1) return code;
     return sandy_launch(decode_shared_merge_kernel<D>, dim3(tiles, n_tokens, (ROWS * D + 127) / 128), dim3(128), 0, stream, (const float*)scratch, splits, out,
                         ld_out, n_heads, n_kv_heads, sink, out_gate);
@@ -325,16 +329,18 @@ SANDY_API long long sandy_decode_attention_shared_scratch(int n_tokens, int n_he
 // q, out: bfloat16 [n_tokens, n_heads * head_dim]; caches bfloat16 [num_pages][n_kv_heads][page_size][head_dim] with
 // page_stride elements between pages (v_cache may be k_cache: one plane); one token per request position (a decode
 // step).  sink: float32 [n_heads] or null; out_gate: float32 [n_tokens, n_heads] or null.  scratch: float32, as many
-// floats as sandy_decode_attention_shared_scratch says (may be null with one split).
-SANDY_API int sandy_decode_attention_shared(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+// floats as sandy_decode_attention_shared_scratch says (may be null with one split).  softcap > 0: a score becomes
+// softcap * tanh(score / softcap); chunk > 0: a query sees only keys j >= pos - pos % chunk.
+SANDY_API int sandy_decode_attention_shared_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
                                             const int* block_table, int max_blocks, const int* token_seq, const int* positions,
                                             void* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                            int page_size, float scale, int window, int splits, int num_pages, const float* sink,
-                                            const float* out_gate, float* scratch, int* status, cudaStream_t stream) {
+                                            int page_size, float scale, int window, float softcap, int chunk, int splits,
+                                            int num_pages, const float* sink, const float* out_gate, float* scratch, int* status,
+                                            cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out) return SANDY_ERR_ARGUMENT;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0 || window < 0 || splits < 1 || splits > 65535 ||
-        n_tokens > 65535 || (splits > 1 && !scratch))
+        n_tokens > 65535 || (splits > 1 && !scratch) || softcap < 0.0f || chunk < 0)
         return SANDY_ERR_UNSUPPORTED;
     if (head_dim % 16 || head_dim < 16 || head_dim > 128 || (ld_q & 1) || (page_stride & 7) ||
         ((uintptr_t)q & 3) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
@@ -342,11 +348,22 @@ SANDY_API int sandy_decode_attention_shared(const void* q, int ld_q, const void*
 #define SANDY_CASE(DD)                                                                                                              \
     case DD:                                                                                                                        \
         return launch<DD>((const bf16*)q, ld_q, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, block_table, max_blocks,  \
-                          token_seq, positions, (bf16*)out, ld_out, n_tokens, n_heads, n_kv_heads, page_size, scale, window, splits, \
-                          num_pages, sink, out_gate, scratch, status, stream)
+                          token_seq, positions, (bf16*)out, ld_out, n_tokens, n_heads, n_kv_heads, page_size, scale, window, softcap, \
+                          chunk, splits, num_pages, sink, out_gate, scratch, status, stream)
     switch (head_dim) {
         SANDY_CASE(16); SANDY_CASE(32); SANDY_CASE(48); SANDY_CASE(64); SANDY_CASE(80); SANDY_CASE(96); SANDY_CASE(112); SANDY_CASE(128);
     }
 #undef SANDY_CASE
     return SANDY_ERR_UNSUPPORTED;
+}
+
+// The same with plain scores and no chunks.
+SANDY_API int sandy_decode_attention_shared(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                            const int* block_table, int max_blocks, const int* token_seq, const int* positions,
+                                            void* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                            int page_size, float scale, int window, int splits, int num_pages, const float* sink,
+                                            const float* out_gate, float* scratch, int* status, cudaStream_t stream) {
+    return sandy_decode_attention_shared_cap(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq, positions, out,
+                                             ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size, scale, window, 0.0f, 0, splits,
+                                             num_pages, sink, out_gate, scratch, status, stream);
 }

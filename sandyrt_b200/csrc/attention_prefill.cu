@@ -81,7 +81,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
                          const bf16* __restrict__ v_cache, long long page_stride,
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
                          const int* __restrict__ kv_before, bf16* __restrict__ out, int ld_out, int n_heads,
-                         int n_kv_heads, int page_size, float scale, int window, int num_pages,
+                         int n_kv_heads, int page_size, float scale, int window, float softcap, int chunk, int num_pages,
                          const float* __restrict__ sink, const float* __restrict__ out_gate,
                          int* __restrict__ status) {
     constexpr int LDS = D + 8;               // row pitch in elements: 16 bytes of padding
@@ -108,7 +108,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
     const int before = kv_before[s];
     const int pos_first = before + t0;
     const int pos_last = pos_first + rows_valid - 1;
-    const int key_lo = window > 0 ? max(0, pos_first + 1 - window) : 0;
+    // the first key any row of the block sees: the window's edge and the start of the first row's chunk of positions
+    int key_lo = window > 0 ? max(0, pos_first + 1 - window) : 0;
+    if (chunk > 0) key_lo = max(key_lo, pos_first - pos_first % chunk);
     const int kt_begin = key_lo / BN, kt_end = pos_last / BN;
     const int kvh = h / (n_heads / n_kv_heads);
     const int* table = block_table + (size_t)s * max_blocks;
@@ -168,8 +170,14 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
     const int rgroup = warp & 3, khalf = warp >> 2;          // which 16 rows, which half of each key tile
     const int row0 = rgroup * 16 + g, row1 = row0 + 8;
     const int pos0 = pos_first + row0, pos1 = pos_first + row1;
-    const int lo0 = window > 0 ? max(0, pos0 + 1 - window) : 0;
-    const int lo1 = window > 0 ? max(0, pos1 + 1 - window) : 0;
+    int lo0 = window > 0 ? max(0, pos0 + 1 - window) : 0;
+    int lo1 = window > 0 ? max(0, pos1 + 1 - window) : 0;
+    if (chunk > 0) {                                         // a row sees the keys of its own chunk only
+        lo0 = max(lo0, pos0 - pos0 % chunk);
+        lo1 = max(lo1, pos1 - pos1 % chunk);
+    }
+    // capped scores: cap * tanh(s * scale / cap), in the softmax's base-2 units
+    const float cap_log2 = softcap * 1.4426950408889634f, over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
 
     uint32_t qa[KSTEPS][4];
     bool q_loaded = false;
@@ -209,12 +217,27 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
         float m_new[2] = {m_run[0], m_run[1]};
         // a tile every row of the block sees whole needs no mask (all tiles but the last one
         // or two of a causal block, when there is no window)
-        const bool whole = kt * BN + BN - 1 <= pos_first && (window == 0 || kt * BN >= pos_last + 1 - window);
+        const bool whole = kt * BN + BN - 1 <= pos_first && (window == 0 || kt * BN >= pos_last + 1 - window) &&
+                           (chunk == 0 || kt * BN >= pos_last - pos_last % chunk);
 #pragma unroll
         for (int nt = 0; nt < BNW / 8; nt++) {
-            if (whole) {
+            if (softcap > 0.0f) {
 #pragma unroll
-                for (int e = 0; e < 4; e++) sc[nt][e] *= scale_log2;
+                for (int e = 0; e < 4; e++) sc[nt][e] = cap_log2 * tanhf(sc[nt][e] * over_cap);
+            }
+            if (whole) {
+                if (softcap <= 0.0f) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) sc[nt][e] *= scale_log2;
+                }
+            } else if (softcap > 0.0f) {
+                const int j0 = kt * BN + khalf * BNW + nt * 8 + 2 * t;
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int j = j0 + e;
+                    if (!(j <= pos0 && j >= lo0)) sc[nt][e] = -INFINITY;
+                    if (!(j <= pos1 && j >= lo1)) sc[nt][2 + e] = -INFINITY;
+                }
             } else {
                 const int j0 = kt * BN + khalf * BNW + nt * 8 + 2 * t;
 #pragma unroll
@@ -337,8 +360,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
 template <int D>
 int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
            const int* block_table, int max_blocks, const int* q_start, const int* kv_before, void* out, int ld_out,
-           int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int page_size, float scale, int window,
-           int num_pages, const float* sink, const float* out_gate, int* status, cudaStream_t stream) {
+           int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int page_size, float scale, int window, float softcap,
+           int chunk, int num_pages, const float* sink, const float* out_gate, int* status, cudaStream_t stream) {
     constexpr int LDS = D + 8;
     const int smem_two = (BM + 2 * STAGES * BN) * LDS * (int)sizeof(bf16);
     const int smem = k_cache == v_cache ? (BM + STAGES * BN) * LDS * (int)sizeof(bf16) : smem_two;
@@ -351,7 +374,8 @@ int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, lo
     dim3 grid((max_q_len + BM - 1) / BM, n_heads, n_seqs);
     prefill_attention_kernel<D><<<grid, THREADS, smem, stream>>>(
         (const bf16*)q, ld_q, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, block_table, max_blocks, q_start,
-        kv_before, (bf16*)out, ld_out, n_heads, n_kv_heads, page_size, scale, window, num_pages, sink, out_gate, status);
+        kv_before, (bf16*)out, ld_out, n_heads, n_kv_heads, page_size, scale, window, softcap, chunk, num_pages, sink, out_gate,
+        status);
     return sandy_launch_status();
 }
 
@@ -359,16 +383,17 @@ int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, lo
 
 // q, out: bfloat16 [n_tokens, H*D]; q_start: int32 [n_seqs + 1], first new token of each request;
 // kv_before: int32 [n_seqs], tokens each request had in the cache before the step;
-// max_q_len: the longest portion (sizes the grid).  Caches, sink and out_gate as in attention.cu.
-SANDY_API int sandy_prefill_attention_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+// max_q_len: the longest portion (sizes the grid).  Caches, sink, out_gate, softcap and chunk as in attention.cu.
+SANDY_API int sandy_prefill_attention_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache,
                                       long long page_stride, const int* block_table, int max_blocks,
                                       const int* q_start, const int* kv_before, void* out, int ld_out, int n_seqs,
                                       int max_q_len, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                      float scale, int window, int num_pages, const float* sink, const float* out_gate,
-                                      int* status, cudaStream_t stream) {
+                                      float scale, int window, float softcap, int chunk, int num_pages, const float* sink,
+                                      const float* out_gate, int* status, cudaStream_t stream) {
     if (n_seqs == 0 || max_q_len == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !q_start || !kv_before || !out) return SANDY_ERR_ARGUMENT;
-    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || page_size <= 0 || window < 0) return SANDY_ERR_UNSUPPORTED;
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || page_size <= 0 || window < 0 || softcap < 0.0f || chunk < 0)
+        return SANDY_ERR_UNSUPPORTED;
     if (page_size & (page_size - 1)) return SANDY_ERR_UNSUPPORTED;      // pages are a power of two long
     if (n_heads > 65535 || n_seqs > 65535) return SANDY_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
@@ -379,10 +404,22 @@ SANDY_API int sandy_prefill_attention_ext(const void* q, int ld_q, const void* k
     if (head_dim == DD)                                                                                         \
         return launch<DD>(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, q_start, kv_before,  \
                           out, ld_out, n_seqs, max_q_len, n_heads, n_kv_heads, page_size, scale, window,        \
-                          num_pages, sink, out_gate, status, stream)
+                          softcap, chunk, num_pages, sink, out_gate, status, stream)
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
 #undef CASE
     return SANDY_ERR_UNSUPPORTED;
+}
+
+// The same with plain scores and no chunks.
+SANDY_API int sandy_prefill_attention_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                      long long page_stride, const int* block_table, int max_blocks,
+                                      const int* q_start, const int* kv_before, void* out, int ld_out, int n_seqs,
+                                      int max_q_len, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                      float scale, int window, int num_pages, const float* sink, const float* out_gate,
+                                      int* status, cudaStream_t stream) {
+    return sandy_prefill_attention_cap(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, q_start, kv_before,
+                                       out, ld_out, n_seqs, max_q_len, n_heads, n_kv_heads, head_dim, page_size, scale,
+                                       window, 0.0f, 0, num_pages, sink, out_gate, status, stream);
 }
 
 // The same without a sink or an output gate.

@@ -116,6 +116,17 @@ int sandy_paged_attention_cap(const void* q, int ld_q, const void* k_cache, cons
                               int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
                               int window, float softcap, int chunk, int num_pages, int dtype, const float* sink,
                               const float* out_gate, int* status, cudaStream_t stream);
+int sandy_prefill_attention_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                const int* block_table, int max_blocks, const int* q_start, const int* kv_before, void* out,
+                                int ld_out, int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int head_dim,
+                                int page_size, float scale, int window, float softcap, int chunk, int num_pages,
+                                const float* sink, const float* out_gate, int* status, cudaStream_t stream);
+int sandy_decode_attention_shared_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                      const int* block_table, int max_blocks, const int* token_seq, const int* positions,
+                                      void* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                      int page_size, float scale, int window, float softcap, int chunk, int splits,
+                                      int num_pages, const float* sink, const float* out_gate, float* scratch, int* status,
+                                      cudaStream_t stream);
 int sandy_decode_attention_cluster_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
                                        const int* block_table, int max_blocks, const int* token_seq, const int* positions,
                                        void* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
