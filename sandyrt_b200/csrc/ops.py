@@ -187,8 +187,10 @@ def kv_append(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions)
 
 
 def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *, sink=None, out_gate=None,
-                    n_heads: int, scale: float, window: int = 0) -> None:
-    """Causal attention of every token of the step over its request's pages (general kernel)."""
+                    n_heads: int, scale: float, window: int = 0, softcap: float = 0.0, chunk: int = 0) -> None:
+    """Causal attention of every token of the step over its request's pages (general kernel).  softcap > 0 presses
+    every score into softcap * tanh(score / softcap); chunk > 0 lets a query see the keys of its own chunk of
+    positions only."""
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
@@ -201,12 +203,13 @@ def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out,
         raise KernelError("attention: q and out must be [T, H*D] of the cache's dtype")
     _i32(block_table, "block_table"); _i32(token_seq, "token_seq"); _i32(positions, "positions")
     lib = load_library("attention")
-    code = lib.sandy_paged_attention_ext(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
+    code = lib.sandy_paged_attention_cap(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
                                      ctypes.c_longlong(page_stride), _p(block_table),
                                      ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
                                      ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(n_heads),
                                      ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale),
-                                     ctypes.c_int(window), ctypes.c_int(num_pages), ctypes.c_int(_dt(q)),
+                                     ctypes.c_int(window), ctypes.c_float(softcap), ctypes.c_int(chunk),
+                                     ctypes.c_int(num_pages), ctypes.c_int(_dt(q)),
                                      _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
     _check(code, f"paged_attention(H={n_heads},Hkv={hkv},D={d})")
 
@@ -303,9 +306,9 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
 
 
 def decode_attention_shared(q, k_cache, v_cache, block_table, token_seq, positions, out, *, n_heads: int, scale: float, splits: int = 1,
-                            window: int = 0, sink=None, out_gate=None) -> None:
+                            window: int = 0, sink=None, out_gate=None, softcap: float = 0.0, chunk: int = 0) -> None:
     """Single-token attention with the query heads of a group as the rows of one tensor-core product (bfloat16, head sizes
-    up to 128); v_cache may be k_cache itself (one plane)."""
+    up to 128); v_cache may be k_cache itself (one plane).  softcap and chunk as in paged_attention."""
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
@@ -313,20 +316,21 @@ def decode_attention_shared(q, k_cache, v_cache, block_table, token_seq, positio
     lib.sandy_decode_attention_shared_scratch.restype = ctypes.c_longlong
     floats = lib.sandy_decode_attention_shared_scratch(ctypes.c_int(T), ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(splits))
     scratch = torch.empty(max(int(floats), 1), dtype=torch.float32, device=q.device)
-    code = lib.sandy_decode_attention_shared(
+    code = lib.sandy_decode_attention_shared_cap(
         _p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache), ctypes.c_longlong(page_stride), _p(block_table),
         ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out), ctypes.c_int(out.stride(0)), ctypes.c_int(T),
         ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window),
-        ctypes.c_int(splits), ctypes.c_int(num_pages), _p(sink), _p(out_gate), _p(scratch), _p(kernel_status(q.device)), _stream())
+        ctypes.c_float(softcap), ctypes.c_int(chunk), ctypes.c_int(splits), ctypes.c_int(num_pages), _p(sink), _p(out_gate), _p(scratch), _p(kernel_status(q.device)), _stream())
     _check(code, f"decode_attention_shared(H={n_heads},Hkv={hkv},D={d})")
 
 
 def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out, *, sink=None, out_gate=None, n_heads: int,
-                      max_q_len: int, scale: float, window: int = 0, tc=None) -> None:
+                      max_q_len: int, scale: float, window: int = 0, tc=None, softcap: float = 0.0, chunk: int = 0) -> None:
     """Tensor-core attention of prompt portions (bfloat16, head sizes 16..128 in steps of 16).
     q_start: int32 [S+1] first new token of each request; kv_before: int32 [S].
     tc: True asks for the tcgen05 kernel (heads of 64), False for the mma.sync kernel, None
-    picks the tcgen05 kernel where it takes the shape."""
+    picks the tcgen05 kernel where it takes the shape.  softcap and chunk as in paged_attention; the mma.sync
+    kernel has the form for them."""
     _cuda(q, k_cache, v_cache, block_table, q_start, kv_before, out, sink, out_gate)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     if q.dtype != torch.bfloat16 or d % 16 != 0 or d > 128:
@@ -345,18 +349,22 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
             ctypes.c_int(out.stride(0)), ctypes.c_int(S), ctypes.c_int(max_q_len), ctypes.c_int(n_heads),
             ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window),
             ctypes.c_int(num_pages), _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
-    if tc or (tc is None and d == 64):
+    ruled = softcap > 0.0 or chunk > 0
+    if tc and ruled:
+        raise UnsupportedShape("prefill_attention: the tcgen05 kernel has no form for capped scores or chunks")
+    if tc or (tc is None and d == 64 and not ruled):
         code = load_library("attention_prefill_tc").sandy_prefill_attention_tc_ext(*args)
         if code != -1 or tc:
             _check(code, f"prefill_attention_tc(H={n_heads},Hkv={hkv},D={d})")
             return
     lib = load_library("attention_prefill")
-    code = lib.sandy_prefill_attention_ext(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
+    code = lib.sandy_prefill_attention_cap(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
                                        ctypes.c_longlong(page_stride), _p(block_table),
                                        ctypes.c_int(block_table.shape[1]), _p(q_start), _p(kv_before), _p(out),
                                        ctypes.c_int(out.stride(0)), ctypes.c_int(S), ctypes.c_int(max_q_len),
                                        ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps),
-                                       ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(num_pages),
+                                       ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_float(softcap),
+                                       ctypes.c_int(chunk), ctypes.c_int(num_pages),
                                        _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
     _check(code, f"prefill_attention(H={n_heads},Hkv={hkv},D={d})")
 
@@ -411,6 +419,54 @@ def glu(a, b, out, act: str = "silu") -> None:
     _check(code, "glu")
 
 
+def glu_clamped(a, b, out, *, limit: float, alpha: float) -> None:
+    """out = g * sigmoid(alpha * g) * (u + 1) with g = min(a, limit) and u = clamp(b, -limit, limit)."""
+    _cuda(a, b, out)
+    if a.shape != b.shape or a.stride(0) != b.stride(0) or a.dtype != b.dtype or out.dtype != a.dtype:
+        raise KernelError("glu_clamped: a and b of one shape, pitch and type expected")
+    code = load_library("elementwise").sandy_glu_clamped(_p(a), _p(b), ctypes.c_int(a.stride(0)), _p(out), ctypes.c_int(out.stride(0)),
+                                                         ctypes.c_int(a.shape[0]), ctypes.c_int(a.shape[1]), ctypes.c_float(limit),
+                                                         ctypes.c_float(alpha), ctypes.c_int(_dt(a)), _stream())
+    _check(code, "glu_clamped")
+
+
+def stream_add(x, x0=None, row=None) -> None:
+    """x += x0 (float32 [rows, cols], optional) + row (float32 [cols], optional)."""
+    _cuda(x, x0, row)
+    for t, n in ((x, "x"), (x0, "x0"), (row, "row")):
+        _f32(t, n)
+    code = load_library("elementwise").sandy_stream_add(_p(x), ctypes.c_int(x.stride(0)), _p(x0), ctypes.c_int(0 if x0 is None else x0.stride(0)),
+                                                        _p(row), ctypes.c_int(x.shape[0]), ctypes.c_int(x.shape[1]), _stream())
+    _check(code, "stream_add")
+
+
+def softcap(x, cap: float) -> None:
+    """x <- cap * tanh(x / cap), float32, in place."""
+    _cuda(x)
+    _f32(x, "x")
+    _check(load_library("elementwise").sandy_softcap_f32(_p(x), ctypes.c_longlong(x.numel()), ctypes.c_float(cap), _stream()), "softcap")
+
+
+def rmsnorm_shift(x, gain, mix, state, token_seq, q_start, seq_slots, out, *, eps: float) -> None:
+    """Token shift behind an RMS norm: h[t] = x[t] / rms(x[t]) * gain; out[t] = h[t] + (h[t-1] - h[t]) * mix, where the h
+    before a request's first token of the step is its row of `state` (float32 [slots, >= width]); afterwards every
+    request's row holds the h of its last token."""
+    _cuda(x, gain, mix, state, token_seq, q_start, seq_slots, out)
+    for t, n in ((x, "x"), (gain, "gain"), (mix, "mix")):
+        _f32(t, n)
+    _i32(token_seq, "token_seq"); _i32(q_start, "q_start"); _i32(seq_slots, "seq_slots")
+    if state.dtype != torch.float32 or state.stride(1) != 1:
+        raise KernelError("rmsnorm_shift: state must be float32 rows")
+    T, W = x.shape
+    S = seq_slots.numel()
+    lib = load_library("rmsnorm")
+    _check(lib.sandy_rmsnorm_shift(_p(x), ctypes.c_int(x.stride(0)), _p(gain), _p(mix), _p(state), ctypes.c_longlong(state.stride(0)),
+                                   _p(token_seq), _p(q_start), _p(seq_slots), _p(out), ctypes.c_int(out.stride(0)), ctypes.c_int(T),
+                                   ctypes.c_int(W), ctypes.c_float(eps), ctypes.c_int(_dt(out)), _stream()), "rmsnorm_shift")
+    _check(lib.sandy_rmsnorm_keep(_p(x), ctypes.c_int(x.stride(0)), _p(gain), _p(state), ctypes.c_longlong(state.stride(0)), _p(q_start),
+                                  _p(seq_slots), ctypes.c_int(S), ctypes.c_int(W), ctypes.c_float(eps), _stream()), "rmsnorm_keep")
+
+
 def scale_add(y, gain, x, y2=None, gain2=None) -> None:
     """x += gain * y (+ gain2 * y2), all float32; gains are [width]."""
     _cuda(y, gain, x, y2, gain2)
@@ -462,6 +518,28 @@ def moe_route(logits, bias, top: int) -> Routing:
     lib = load_library("moe")
     _check(lib.sandy_moe_route(_p(logits), ctypes.c_int(logits.stride(0)), _p(bias), ctypes.c_int(T), ctypes.c_int(E), ctypes.c_int(top),
                                _p(r.expert_of), _p(r.weight_of), _stream()), f"moe_route(E={E},top={top})")
+    _check(lib.sandy_moe_group(_p(r.expert_of), ctypes.c_int(T * top), ctypes.c_int(E), _p(r.group_start), _p(r.entry_of_slot),
+                               _p(r.slot_of_entry), _stream()), "moe_group")
+    return r
+
+
+def moe_route_scored(logits, correction, top: int, *, n_groups: int = 1, keep_groups: int = 1, group_rank: int = 2,
+                     weight_scale: float = 1.0, norm_eps: float = 0.0) -> Routing:
+    """Routing by sigmoid scores: choice scores are the scores plus `correction`; experts form `n_groups` groups of
+    neighbours, a group's score is the sum of its `group_rank` largest choice scores, only the `keep_groups` best groups
+    can be chosen from; the `top` largest choice scores win, weighted by their plain scores over their sum (+ norm_eps)
+    times weight_scale.  Then the entries grouped by expert."""
+    _cuda(logits, correction)
+    _f32(logits, "logits"); _f32(correction, "correction")
+    T, E = logits.shape
+    dev = logits.device
+    i32 = lambda n: torch.empty(n, dtype=torch.int32, device=dev)
+    r = Routing(T, E, top, i32(T * top), torch.empty(T * top, dtype=torch.float32, device=dev), i32(E + 1), i32(T * top), i32(T * top))
+    lib = load_library("moe")
+    _check(lib.sandy_moe_route_scored(_p(logits), ctypes.c_int(logits.stride(0)), _p(correction), ctypes.c_int(T), ctypes.c_int(E),
+                                      ctypes.c_int(top), ctypes.c_int(n_groups), ctypes.c_int(keep_groups), ctypes.c_int(group_rank),
+                                      ctypes.c_float(weight_scale), ctypes.c_float(norm_eps), _p(r.expert_of), _p(r.weight_of), _stream()),
+           f"moe_route_scored(E={E},top={top},groups={n_groups},keep={keep_groups})")
     _check(lib.sandy_moe_group(_p(r.expert_of), ctypes.c_int(T * top), ctypes.c_int(E), _p(r.group_start), _p(r.entry_of_slot),
                                _p(r.slot_of_entry), _stream()), "moe_group")
     return r
