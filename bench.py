@@ -457,10 +457,27 @@ def latent_config(width, heads, kv_heads, ff, vocab=50257, layers=4):
             "layers": [{**order[i % 4][0], "mlp": order[i % 4][1]} for i in range(layers)]}
 
 
-def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int, design: str = "panupel") -> int:
-    """Prefill and decode throughput of a design (Panupel or Sovezen) at sizes that resemble real layers, beside GPT-2
-    with the same width, heads, layer count and vocabulary, both with random weights; then the device time per kernel
-    class of both, so that like kernels can be held against each other.  One JSON line per size, then the tables."""
+# ---- capped attention in chunks behind a token shift (Bilurax) beside Sovezen at equal size ---------------------
+# Heads of 64 on a quarter as many key/value heads, scores capped at 30, chunks of `chunk` positions (1,024 by default:
+# the longest context this comparison runs, so the attention kernels read as many keys as the other design's; a
+# smaller chunk shows what skipping the keys of other chunks saves).  The dense feed-forward has two matrices of
+# 3/2 x ff against the other design's three of ff; the routed one has 16 clamped gated experts of ff / 2 in 4 groups,
+# 2 groups kept and 2 experts run, so both designs move the same weights a token.
+def capped_config(width, heads, kv_heads, ff, vocab=50257, layers=4, chunk=1024):
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125,
+                                          "softcap": 30.0, "mask": {"size": chunk}}}
+    dense = {"kind": "dense", "ff": ff * 3 // 2}
+    moe = {"kind": "moe", "expert": {"ff": ff // 2, "limit": 7.0},
+           "router": {"experts": 16, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    return {"architecture": "Bilurax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "embedding": {"scale": 1.0}, "layers": [{**att, "mlp": dense if i % 2 == 0 else moe} for i in range(layers)]}
+
+
+def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int, design: str = "panupel", chunk: int = 1024) -> int:
+    """Prefill and decode throughput of a design (Panupel, Sovezen or Bilurax) at sizes that resemble real layers,
+    beside its closest relative with the same width, heads, layer count and vocabulary (GPT-2; for Bilurax, Sovezen),
+    both with random weights; then the device time per kernel class of both, so that like kernels can be held against
+    each other.  One JSON line per size, then the tables."""
     import numpy as np
     import torch
 
@@ -471,11 +488,18 @@ def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int, de
     peaks = load_peaks()
     layers = layers or 4
     rng = np.random.default_rng(0)
-    hybrid_config = {"panupel": globals()["hybrid_config"], "sovezen": latent_config}[design]
-    for name, sz in HYBRID_SIZES.items():
+    hybrid_config = {"panupel": globals()["hybrid_config"], "sovezen": latent_config,
+                     "bilurax": lambda **kw: capped_config(chunk=chunk, **kw)}[design]
+
+    def arms(sz):
+        if design == "bilurax":
+            return ((design, hybrid_config(layers=layers, **sz)), ("sovezen", latent_config(layers=layers, **sz)))
         gpt2_raw = {**load_model_config("small"), "n_embd": sz["width"], "n_head": sz["heads"], "n_inner": None, "n_layer": layers}
+        return ((design, hybrid_config(layers=layers, **sz)), ("gpt2", gpt2_raw))
+
+    for name, sz in HYBRID_SIZES.items():
         out = {"size": name, "layers": layers, "dtype": dtype_name, "data": "synthetic", "peaks": peaks["source"]}
-        for arch, raw in ((design, hybrid_config(layers=layers, **sz)), ("gpt2", gpt2_raw)):
+        for arch, raw in arms(sz):
             cfg = config_from_normalised(raw)
             cfg.validate()
             model = build_model(cfg)
@@ -496,8 +520,7 @@ def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int, de
         print(json.dumps(out), flush=True)
     # per kernel class, eager launches with events around each
     for name, sz in HYBRID_SIZES.items():
-        gpt2_raw = {**load_model_config("small"), "n_embd": sz["width"], "n_head": sz["heads"], "n_inner": None, "n_layer": layers}
-        for arch, raw in ((design, hybrid_config(layers=layers, **sz)), ("gpt2", gpt2_raw)):
+        for arch, raw in arms(sz):
             print(f"---- {arch}, width {name} ----")
             kernel_table(config_from_normalised(raw), dtype_name, batch)
     return 0
@@ -525,6 +548,9 @@ def main() -> int:
                     help="Panupel beside GPT-2 at equal sizes: decode and prefill throughput, then time per kernel class")
     ap.add_argument("--latent", action="store_true",
                     help="Sovezen (attention over a latent, routed experts) beside GPT-2 at equal sizes, as --hybrid does for Panupel")
+    ap.add_argument("--capped", action="store_true",
+                    help="Bilurax (capped attention in chunks behind a token shift, grouped routing) beside Sovezen at equal sizes")
+    ap.add_argument("--chunk", type=int, default=1024, help="chunk of positions of --capped")
     ap.add_argument("--micro", nargs=argparse.REMAINDER, help="run a kernel micro-benchmark (see sandyrt_b200/csrc/microbench.py)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -535,9 +561,9 @@ def main() -> int:
     if args.micro is not None:
         from sandyrt_b200.csrc import microbench
         return microbench.main(args.micro)
-    if args.hybrid or args.latent:
+    if args.hybrid or args.latent or args.capped:
         return hybrid(args.dtype, args.layers, args.batch, min(args.steps, 128), args.warmup,
-                      design="sovezen" if args.latent else "panupel")
+                      design="bilurax" if args.capped else "sovezen" if args.latent else "panupel", chunk=args.chunk)
     if args.workload:
         return workload(args.workload, args.dtype, args.layers)
     if args.profile_kernels:
