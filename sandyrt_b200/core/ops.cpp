@@ -499,12 +499,12 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     const std::string shape = "(H=" + std::to_string(n_heads) + ",Hkv=" + std::to_string(hkv) + ",D=" + std::to_string(d) + ")";
     if (s.max_q_len > 1 && q.dtype == DType::BF16 && d <= 128) {
         static const bool use_tc = env_int("SANDYRT_PREFILL_TC", 1) != 0;     // 0 keeps every head size on the mma.sync kernel
-        if (use_tc && d == 64 && !ruled) {
-            static auto fn = SANDY_KERNEL(attention_prefill_tc, sandy_prefill_attention_tc_ext);
+        if (use_tc && d == 64) {
+            static auto fn = SANDY_KERNEL(attention_prefill_tc, sandy_prefill_attention_tc_cap);
             OpTimer timer(l, "attention, prompt (tcgen05)", attn_bytes, attn_flops);
             const int code = fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.q_start, s.kv_before,
                                 out.data, (int)out.ld, s.n_seqs, s.max_q_len, n_heads, hkv, d, c.page_size, scale, window,
-                                c.num_pages, sk, og, l.kernel_status, l.stream);
+                                cap, chunk, c.num_pages, sk, og, l.kernel_status, l.stream);
             if (code != -1) { check(code, "prefill_attention_tc" + shape); return; }
         }
         static auto fn = SANDY_KERNEL(attention_prefill, sandy_prefill_attention_cap);

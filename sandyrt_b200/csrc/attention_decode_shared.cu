@@ -162,7 +162,7 @@ decode_shared_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __restric
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const int key = key0 + nt * 8 + tq * 2 + (j & 1);
-                const float sc = softcap > 0.0f ? cap2 * tanhf(s[nt][j] * over_cap) : s[nt][j] * s2;
+                const float sc = softcap > 0.0f ? cap2 * tanh_fast(s[nt][j] * over_cap) : s[nt][j] * s2;
                 s[nt][j] = key <= pos ? sc : -INFINITY;
             }
         unsigned pa[4];

@@ -223,7 +223,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
         for (int nt = 0; nt < BNW / 8; nt++) {
             if (softcap > 0.0f) {
 #pragma unroll
-                for (int e = 0; e < 4; e++) sc[nt][e] = cap_log2 * tanhf(sc[nt][e] * over_cap);
+                for (int e = 0; e < 4; e++) sc[nt][e] = cap_log2 * tanh_fast(sc[nt][e] * over_cap);
             }
             if (whole) {
                 if (softcap <= 0.0f) {

@@ -49,7 +49,8 @@
 //
 // Like every attention kernel here it reads all keys from the cache (the step's own keys are
 // appended first): query i of a portion sits at position kv_before + i and sees keys
-// max(0, pos+1-window) .. pos.  Softmax statistics and the accumulator are float; P is rounded
+// max(0, pos+1-window) .. pos; with chunk > 0 only those from pos - pos % chunk on, and with softcap > 0
+// a score s becomes softcap * tanh(s / softcap) before the softmax.  Softmax statistics and the accumulator are float; P is rounded
 // to bfloat16 for the product (the row sum is taken before rounding).
 //
 // Every wait on an mbarrier is bounded; a wait that runs out raises bit 8 of the status word
@@ -156,14 +157,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+template <bool CAPPED>      // whether scores are capped: layers without a cap keep the code they had
 __global__ void __launch_bounds__(THREADS, 2)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const bf16* __restrict__ q, int ld_q, const bf16* __restrict__ k_cache,
                             const bf16* __restrict__ v_cache, long long page_stride,
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
                             const int* __restrict__ kv_before, bf16* __restrict__ out, int ld_out, int n_heads,
-                            int n_kv_heads, int page_size, float scale, int window, int num_pages,
-                            int use_tma, const float* __restrict__ sink, const float* __restrict__ out_gate,
+                            int n_kv_heads, int page_size, float scale, int window, float softcap, int chunk,
+                            int num_pages, int use_tma, const float* __restrict__ sink, const float* __restrict__ out_gate,
                             int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_table[TABLE_SMEM];
@@ -188,7 +190,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int before = kv_before[s];
     const int pos_first = before + t0;
     const int pos_last = pos_first + rows_valid - 1;
-    const int key_lo = window > 0 ? max(0, pos_first + 1 - window) : 0;
+    int key_lo = window > 0 ? max(0, pos_first + 1 - window) : 0;
+    if (chunk > 0) key_lo = max(key_lo, pos_first - pos_first % chunk);      // the first row's chunk starts first
     const int kt_begin = key_lo / BN, kt_end = pos_last / BN;
     const int n_it = kt_end - kt_begin + 1;
     const int kvh = h / (n_heads / n_kv_heads);
@@ -387,7 +390,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         float m_ref = -INFINITY, l_run = 0.0f;  // the maximum the row's exponentials refer to; the row's sum
         const float scale_log2 = scale * 1.4426950408889634f;
         const int pos = pos_first + row;
-        const int lo = window > 0 ? max(0, pos + 1 - window) : 0;
+        int lo = window > 0 ? max(0, pos + 1 - window) : 0;
+        if (chunk > 0) lo = max(lo, pos - pos % chunk);      // a row sees the keys of its own chunk only
+        // capped scores: S holds q.k, and what reaches the exponent is S * scale; so S becomes (cap / scale) *
+        // tanh(S * scale / cap), before the mask (whose -inf the tanh would turn into -cap)
+        const float over_cap = CAPPED ? scale / softcap : 0.0f, cap_over = CAPPED ? softcap / scale : 0.0f;
 
         for (int it = 0; it < n_it; it++) {
             const int kt = kt_begin + it;
@@ -402,8 +409,16 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             bar_arrive(BAR_S_READ, THREADS);
 
             // a tile every row of the block sees whole needs no mask
-            const bool whole = kt * BN + BN - 1 <= pos_first && (window == 0 || kt * BN >= pos_last + 1 - window);
+            const bool whole = kt * BN + BN - 1 <= pos_first && (window == 0 || kt * BN >= pos_last + 1 - window) &&
+                               (chunk == 0 || kt * BN >= pos_last - pos_last % chunk);
             const int j0 = kt * BN + half * 64;
+            if (CAPPED) {
+#pragma unroll
+                for (int e = 0; e < 32; e++) {
+                    sa[e] = __float_as_uint(cap_over * tanh_fast(__uint_as_float(sa[e]) * over_cap));
+                    sb[e] = __float_as_uint(cap_over * tanh_fast(__uint_as_float(sb[e]) * over_cap));
+                }
+            }
             if (!whole) {
 #pragma unroll
                 for (int e = 0; e < 32; e++) {
@@ -557,16 +572,17 @@ bool get_page_map(const void* cache, long long page_stride, int num_pages, int n
 // Arguments as sandy_prefill_attention (attention_prefill.cu).  Heads of 64 only; out and q rows
 // must be 16-byte aligned.  SANDY_ERR_UNSUPPORTED for everything else: the caller then takes the
 // mma.sync kernel.
-SANDY_API int sandy_prefill_attention_tc_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+SANDY_API int sandy_prefill_attention_tc_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache,
                                          long long page_stride, const int* block_table, int max_blocks,
                                          const int* q_start, const int* kv_before, void* out, int ld_out, int n_seqs,
                                          int max_q_len, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                         float scale, int window, int num_pages, const float* sink,
-                                         const float* out_gate, int* status, cudaStream_t stream) {
+                                         float scale, int window, float softcap, int chunk, int num_pages,
+                                         const float* sink, const float* out_gate, int* status, cudaStream_t stream) {
     if (n_seqs == 0 || max_q_len == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !q_start || !kv_before || !out) return SANDY_ERR_ARGUMENT;
     if (head_dim != HD) return SANDY_ERR_UNSUPPORTED;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || page_size <= 0 || window < 0) return SANDY_ERR_UNSUPPORTED;
+    if (softcap < 0.0f || chunk < 0 || (softcap > 0.0f && !(scale > 0.0f))) return SANDY_ERR_UNSUPPORTED;
     if (page_size & (page_size - 1)) return SANDY_ERR_UNSUPPORTED;      // pages are a power of two long
     if (n_heads > 65535 || n_seqs > 65535) return SANDY_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
@@ -585,16 +601,30 @@ SANDY_API int sandy_prefill_attention_tc_ext(const void* q, int ld_q, const void
     }
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(prefill_attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid((max_q_len + BM - 1) / BM, n_heads, n_seqs);
-    return sandy_launch(prefill_attention_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mk, mv, (const bf16*)q, ld_q,
+    return sandy_launch(softcap > 0.0f ? prefill_attention_tc_kernel<true> : prefill_attention_tc_kernel<false>, grid, dim3(THREADS), SMEM_BYTES, stream, mk, mv, (const bf16*)q, ld_q,
                         (const bf16*)k_cache, (const bf16*)v_cache, page_stride, block_table, max_blocks, q_start,
-                        kv_before, (bf16*)out, ld_out, n_heads, n_kv_heads, page_size, scale, window, num_pages, use_tma,
-                        sink, out_gate, status);
+                        kv_before, (bf16*)out, ld_out, n_heads, n_kv_heads, page_size, scale, window, softcap, chunk, num_pages,
+                        use_tma, sink, out_gate, status);
+}
+
+// The same without capped scores or chunks.
+SANDY_API int sandy_prefill_attention_tc_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                         long long page_stride, const int* block_table, int max_blocks,
+                                         const int* q_start, const int* kv_before, void* out, int ld_out, int n_seqs,
+                                         int max_q_len, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                         float scale, int window, int num_pages, const float* sink,
+                                         const float* out_gate, int* status, cudaStream_t stream) {
+    return sandy_prefill_attention_tc_cap(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, q_start,
+                                          kv_before, out, ld_out, n_seqs, max_q_len, n_heads, n_kv_heads, head_dim,
+                                          page_size, scale, window, 0.0f, 0, num_pages, sink, out_gate, status, stream);
 }
 
 // The same without a sink or an output gate.

@@ -329,8 +329,8 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
     """Tensor-core attention of prompt portions (bfloat16, head sizes 16..128 in steps of 16).
     q_start: int32 [S+1] first new token of each request; kv_before: int32 [S].
     tc: True asks for the tcgen05 kernel (heads of 64), False for the mma.sync kernel, None
-    picks the tcgen05 kernel where it takes the shape.  softcap and chunk as in paged_attention; the mma.sync
-    kernel has the form for them."""
+    picks the tcgen05 kernel where it takes the shape.  softcap and chunk as in paged_attention; both kernels
+    have the form for them."""
     _cuda(q, k_cache, v_cache, block_table, q_start, kv_before, out, sink, out_gate)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     if q.dtype != torch.bfloat16 or d % 16 != 0 or d > 128:
@@ -348,12 +348,10 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
             _p(block_table), ctypes.c_int(block_table.shape[1]), _p(q_start), _p(kv_before), _p(out),
             ctypes.c_int(out.stride(0)), ctypes.c_int(S), ctypes.c_int(max_q_len), ctypes.c_int(n_heads),
             ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window),
+            ctypes.c_float(softcap), ctypes.c_int(chunk),
             ctypes.c_int(num_pages), _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
-    ruled = softcap > 0.0 or chunk > 0
-    if tc and ruled:
-        raise UnsupportedShape("prefill_attention: the tcgen05 kernel has no form for capped scores or chunks")
-    if tc or (tc is None and d == 64 and not ruled):
-        code = load_library("attention_prefill_tc").sandy_prefill_attention_tc_ext(*args)
+    if tc or (tc is None and d == 64):
+        code = load_library("attention_prefill_tc").sandy_prefill_attention_tc_cap(*args)
         if code != -1 or tc:
             _check(code, f"prefill_attention_tc(H={n_heads},Hkv={hkv},D={d})")
             return

@@ -148,6 +148,75 @@ rmsnorm_shift_kernel(const float* __restrict__ x, int ldx, const float* __restri
     }
 }
 
+// The same with the rows in registers: NV rounds of the block's threads cover the width, weights are asked for before
+// the wait for the kernel that produces x, every row is read once, and the second sum is formed only where the
+// token before is in the step.  Sums run in the order of the kernel above.
+template <typename TO, int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_shift_reg_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ gain, const float* __restrict__ mix,
+                         float* __restrict__ state, long long state_stride, const int* __restrict__ token_seq,
+                         const int* __restrict__ q_start, const int* __restrict__ seq_slots, TO* __restrict__ out, int ldo,
+                         int width, float eps) {
+    __shared__ float scratch[32], scratch_prev[32];
+    const int t = blockIdx.x;
+    const int s = token_seq[t];
+    const int first = q_start[s], last = q_start[s + 1] - 1;
+    float* srow = state + (long long)seq_slots[s] * state_stride;
+    const bool inside = t > first;                   // the token before is a row of this step
+    float g[NV], m[NV];
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        const int e = i * blockDim.x + threadIdx.x;
+        g[i] = (gain && e < width) ? gain[e] : 1.0f;
+        m[i] = e < width ? mix[e] : 0.0f;
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    const float* row = x + (size_t)t * ldx;
+    const float* prow = inside ? row - ldx : srow;
+    float v[NV], p[NV];
+    float ss = 0.0f, sp = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        const int e = i * blockDim.x + threadIdx.x;
+        v[i] = e < width ? row[e] : 0.0f;
+        p[i] = e < width ? prow[e] : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        ss = fmaf(v[i], v[i], ss);
+        sp = fmaf(p[i], p[i], sp);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+    const float inv_prev = inside ? 1.0f / sqrtf(block_sum(sp, scratch_prev) / (float)width + eps) : 0.0f;
+    TO* orow = out + (size_t)t * ldo;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        const int e = i * blockDim.x + threadIdx.x;
+        if (e < width) {
+            const float h = v[i] * inv * g[i];
+            const float before = inside ? p[i] * inv_prev * g[i] : p[i];
+            orow[e] = from_f32<TO>(h + (before - h) * m[i]);
+            if (first == last) srow[e] = h;
+        }
+    }
+}
+
+template <typename TO>
+int launch_shift(const float* x, int ldx, const float* gain, const float* mix, float* state, long long state_stride,
+                 const int* token_seq, const int* q_start, const int* seq_slots, TO* out, int ldo, int n_tokens, int width,
+                 float eps, cudaStream_t stream) {
+    const int threads = width >= 1024 ? 256 : 128;
+#define CASE(NV)                                                                                                          \
+    if (width <= threads * NV)                                                                                            \
+        return sandy_launch(rmsnorm_shift_reg_kernel<TO, NV>, dim3(n_tokens), dim3(threads), 0, stream, x, ldx, gain, mix, \
+                            state, state_stride, token_seq, q_start, seq_slots, out, ldo, width, eps)
+    CASE(2); CASE(4); CASE(6); CASE(8); CASE(16);
+#undef CASE
+    return sandy_launch(rmsnorm_shift_kernel<TO>, dim3(n_tokens), dim3(threads), 0, stream, x, ldx, gain, mix, state,
+                        state_stride, token_seq, q_start, seq_slots, out, ldo, width, eps);
+}
+
 // A block per request of the step; requests with one token were served by the kernel above.
 __global__ void __launch_bounds__(256)
 keep_last_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ gain, float* __restrict__ state,
@@ -271,13 +340,12 @@ SANDY_API int sandy_rmsnorm_shift(const float* x, int ldx, const float* gain, co
     if (n_tokens == 0) return SANDY_OK;
     if (!x || !mix || !state || !token_seq || !q_start || !seq_slots || !out || width <= 0 || state_stride < width)
         return SANDY_ERR_ARGUMENT;
-    const int threads = width >= 1024 ? 256 : 128;
     if (out_dtype == SANDY_F32)
-        return sandy_launch(rmsnorm_shift_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, x, ldx, gain, mix, state,
-                            state_stride, token_seq, q_start, seq_slots, (float*)out, ldo, width, eps);
+        return launch_shift(x, ldx, gain, mix, state, state_stride, token_seq, q_start, seq_slots, (float*)out, ldo, n_tokens,
+                            width, eps, stream);
     if (out_dtype == SANDY_BF16)
-        return sandy_launch(rmsnorm_shift_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, x, ldx, gain, mix, state,
-                            state_stride, token_seq, q_start, seq_slots, (bf16*)out, ldo, width, eps);
+        return launch_shift(x, ldx, gain, mix, state, state_stride, token_seq, q_start, seq_slots, (bf16*)out, ldo, n_tokens,
+                            width, eps, stream);
     return SANDY_ERR_UNSUPPORTED;
 }
 

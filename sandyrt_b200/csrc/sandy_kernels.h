@@ -157,6 +157,11 @@ int sandy_prefill_attention_tc_ext(const void* q, int ld_q, const void* k_cache,
                                    void* out, int ld_out, int n_seqs, int max_q_len, int n_heads, int n_kv_heads,
                                    int head_dim, int page_size, float scale, int window, int num_pages, const float* sink,
                                    const float* out_gate, int* status, cudaStream_t stream);
+int sandy_prefill_attention_tc_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                   const int* block_table, int max_blocks, const int* q_start, const int* kv_before,
+                                   void* out, int ld_out, int n_seqs, int max_q_len, int n_heads, int n_kv_heads,
+                                   int head_dim, int page_size, float scale, int window, float softcap, int chunk,
+                                   int num_pages, const float* sink, const float* out_gate, int* status, cudaStream_t stream);
 
 /* attention_decode_shared.cu */
 long long sandy_decode_attention_shared_scratch(int n_tokens, int n_heads, int n_kv_heads, int head_dim, int splits);
