@@ -398,15 +398,15 @@ def test_the_experts_clamp(tmp_path, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_heads_of_64_in_long_prompts(tmp_path, dtype):
-    """Heads of 64 take the tcgen05 prompt kernel in bfloat16: chunks of 200 and 96 positions cut through its tiles of 128
+    """Heads of 64 take the tcgen05 prompt kernel in bfloat16: chunks of 210 and 96 positions cut through its tiles of 128
     queries and 128 keys, portions start inside chunks and tiles, then single tokens pass a chunk's edge."""
-    cfg = _config(97, 128, [layer(attention(4, 2, 64, 64, 200, softcap=10.0), dense(64)),
+    cfg = _config(97, 128, [layer(attention(4, 2, 64, 64, 210, softcap=10.0), dense(64)),
                             layer(attention(2, 1, 64, 64, 96, softcap=25.0), None)], eps=1e-5, logit_softcap=20.0)
     w, path = _one_model(tmp_path, cfg, seed=21)
     eng = _engine(path, dtype, max_tokens=1024)
     ids = _tokens(cfg, 420, seed=2)
     _check(_run_cuts(eng, "r", ids, [420]), (cfg, w), ids, dtype, "heads of 64, whole")
-    _check(_run_cuts(eng, "r", ids, [130, 2, 199, 70] + [1] * 19), (cfg, w), ids, dtype, "heads of 64, portions and single tokens")
+    _check(_run_cuts(eng, "r", ids, [130, 2, 209, 60] + [1] * 19), (cfg, w), ids, dtype, "heads of 64, portions and single tokens")
 
 
 def test_options_at_their_edges(tmp_path):

@@ -53,14 +53,14 @@ def _want_rows(q, keys, values, positions, H, scale, cap, chunk, window=0):
     return out
 
 
-# portions: (keys before the portion, tokens of the portion); the chunks of 24 / 100 / 128 / 200 positions cut through
+# portions: (keys before the portion, tokens of the portion); the chunks of 24 / 100 / 128 / 210 positions cut through
 # the kernels' tiles of 64 and 128 queries and 128 keys, through pages, and through the portions themselves
-PORTIONS = [(0, 1), (0, 300), (37, 150), (199, 3), (200, 130), (511, 2)]
+PORTIONS = [(0, 1), (0, 300), (37, 150), (209, 3), (210, 130), (511, 2)]
 
 
 @pytest.mark.parametrize("kernel", ["tcgen05", "mma.sync", "general"])
 @pytest.mark.parametrize("H,Hkv,D,cap,chunk,window", [
-    (4, 2, 64, 20.0, 200, 0), (6, 1, 64, 8.0, 24, 0), (2, 2, 64, 0.0, 128, 0), (3, 1, 64, 30.0, 0, 0), (4, 4, 64, 12.0, 100, 70),
+    (4, 2, 64, 18.0, 210, 0), (6, 1, 64, 8.0, 24, 0), (2, 2, 64, 0.0, 128, 0), (3, 1, 64, 30.0, 0, 0), (4, 4, 64, 12.0, 100, 70),
     (2, 1, 96, 15.0, 100, 0), (2, 2, 32, 10.0, 24, 0),
 ])
 def test_prompt_portions_with_capped_scores_in_chunks(kernel, H, Hkv, D, cap, chunk, window):
@@ -95,12 +95,12 @@ def test_prompt_portions_with_capped_scores_in_chunks(kernel, H, Hkv, D, cap, ch
         assert torch.allclose(got, want, atol=3e-2, rtol=3e-2), (r, float((got - want).abs().max()))
 
 
-@pytest.mark.parametrize("H,Hkv,D,cap,chunk,splits", [(6, 1, 96, 20.0, 200, 3), (4, 2, 64, 8.0, 24, 1), (8, 1, 128, 0.0, 100, 4),
+@pytest.mark.parametrize("H,Hkv,D,cap,chunk,splits", [(5, 1, 80, 18.0, 210, 3), (4, 2, 64, 8.0, 24, 1), (8, 1, 128, 0.0, 100, 4),
                                                       (5, 5, 16, 30.0, 0, 2), (12, 2, 48, 6.0, 7, 1)])
 def test_single_tokens_with_capped_scores_in_chunks(H, Hkv, D, cap, chunk, splits):
     """Decoded tokens at the first and the last position of a chunk, one behind an edge, and far into a long request."""
     g = torch.Generator().manual_seed(H * 10 + D)
-    lens = [1, 24, 25, 200, 201, 399, 400, 401, 777]
+    lens = [1, 24, 25, 100, 101, 210, 211, 419, 420, 421, 777]
     keys = [torch.randn(n, Hkv, D, generator=g).to(torch.bfloat16).to(DEV) for n in lens]
     values = [torch.randn(n, Hkv, D, generator=g).to(torch.bfloat16).to(DEV) for n in lens]
     k_view, v_view, table = _paged(keys, values, 16, seed=D)
