@@ -245,6 +245,15 @@ std::map<std::string, Architecture>& table() {
             return describe_bilurax(*g);
         };
         t[bilurax.name] = std::move(bilurax);
+        Architecture tifepel;
+        tifepel.name = TifepelConfig::kArchitecture;
+        tifepel.parse = [](const Json& raw) { return std::unique_ptr<ModelConfig>(new TifepelConfig(TifepelConfig::from_json(raw))); };
+        tifepel.describe = [](const ModelConfig& c) {
+            const auto* g = dynamic_cast<const TifepelConfig*>(&c);
+            if (!g) throw ConfigError("Tifepel was given another architecture's configuration");
+            return describe_tifepel(*g);
+        };
+        t[tifepel.name] = std::move(tifepel);
     });
     return t;
 }

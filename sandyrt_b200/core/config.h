@@ -142,6 +142,34 @@ public:
     void validate() const override;
 };
 
+// Tifepel's config.json (core/tifepel.cpp says what the keys mean): layers listed one by one, each an attention with
+// a bias by distance or a state-space mixer, inside hyper-connections over several copies of the stream, with a short
+// convolution on every sublayer's input and a gate on its result; routed feed-forwards; a span that may run several times.
+class TifepelConfig : public ModelConfig {
+public:
+    static constexpr const char* kArchitecture = "Tifepel";
+    struct Layer {
+        std::string type;                                   // "attention" | "mamba2"
+        int64_t heads = 0, vdim = 0;
+        int64_t kv_heads = 0, dim = 0, bias_max = 0, bias_rows = 0, q_temp_every = 0;      // attention (bias_rows 0: the file's)
+        double scale = 1.0, q_temp_coef = 0.0;
+        int64_t groups = 0, state = 0, conv = 0, norm_groups = 1;                           // mamba2
+        std::string mlp;                                    // "moe" | "" (no feed-forward)
+        int64_t ff = 0, experts = 0, identity = 0, top = 0, shared_ff = 0;
+    };
+    int64_t vocab = 0, width = 0, max_positions = 0, streams = 1, canon_taps = 1;
+    int64_t bigram_buckets = 0, bigram_mul_prev = 0, bigram_mul_cur = 0;
+    double norm_eps = 1e-5;
+    std::vector<Layer> layers;
+    bool has_loop = false;
+    int64_t loop_start = 0, loop_stop = 0, loop_times = 1;
+
+    static TifepelConfig from_json(const Json& raw);
+    std::string architecture() const override { return kArchitecture; }
+    Json to_json() const override;
+    void validate() const override;
+};
+
 // A configuration of an architecture defined outside this library: its normalised config.json
 // as the architecture's own `parse` returned it.
 class ForeignConfig : public ModelConfig {
@@ -178,5 +206,6 @@ ModelSpec describe_gpt2(const GPT2Config& cfg);
 ModelSpec describe_panupel(const PanupelConfig& cfg);
 ModelSpec describe_sovezen(const SovezenConfig& cfg);
 ModelSpec describe_bilurax(const BiluraxConfig& cfg);
+ModelSpec describe_tifepel(const TifepelConfig& cfg);
 
 }  // namespace sandy

@@ -11,6 +11,7 @@ Model::Model(ModelSpec spec) : spec_(std::move(spec)) {
         p.mixer = make_part<Mixer>("mixer", l.mixer);
         p.feed_forward = make_part<FeedForward>("feed_forward", l.feed_forward);
         for (const auto& kv : l.norms) p.norms[kv.first] = make_part<Norm>("norm", kv.second);
+        for (const auto& kv : l.wraps) p.wraps[kv.first] = make_part<Wrap>("wrap", kv.second);
         std::string missing;
         for (const auto& n : bf.norm_names)
             if (!p.norms.count(n)) missing += (missing.empty() ? "" : ", ") + n;
@@ -23,7 +24,12 @@ Model::Model(ModelSpec spec) : spec_(std::move(spec)) {
     final_norm_ = make_part<Norm>("norm", spec_.final_norm);
     head_ = make_part<Head>("head", spec_.head);
     for (const PartSpec& r : spec_.remixes) remixes_.push_back(make_part<Remix>("remix", r));
+    if (spec_.streams < 1) throw ConfigError("a model has at least one residual stream");
+    if (spec_.streams > 1 && !remixes_.empty()) throw ConfigError("stream mixes between layers work on one residual stream");
+    if ((spec_.embedding_cache >= 0) != embedding_->cache_spec().has_state())
+        throw ConfigError("the embedding's state and the cache entry named for it do not go together");
     for (const LayerCall& c : spec_.schedule) {
+        if (c.cache == spec_.embedding_cache) throw ConfigError("a layer uses the embedding's cache entry");
         if (c.layer < 0 || c.layer >= (int)blocks_.size())
             throw ConfigError("run order names layer " + std::to_string(c.layer) + ", the model has " + std::to_string(blocks_.size()));
         if (c.remix >= (int)remixes_.size())
@@ -40,6 +46,7 @@ std::vector<Model::PartRef> Model::parts() const {
         out.push_back({&blocks_[i]->mixer(), &l.mixer});
         out.push_back({&blocks_[i]->feed_forward(), &l.feed_forward});
         for (auto& kv : blocks_[i]->norms()) out.push_back({kv.second.get(), &l.norms.at(kv.first)});
+        for (auto& kv : blocks_[i]->wraps()) out.push_back({kv.second.get(), &l.wraps.at(kv.first)});
     }
     for (size_t i = 0; i < remixes_.size(); i++) out.push_back({remixes_[i].get(), &spec_.remixes[i]});
     out.push_back({final_norm_.get(), &spec_.final_norm});
@@ -82,12 +89,13 @@ std::vector<CacheSpec> Model::cache_specs() const {
     std::vector<CacheSpec> specs((size_t)spec_.n_caches());
     std::vector<char> seen(specs.size(), 0);
     for (const LayerCall& c : spec_.schedule) {
-        const CacheSpec s = blocks_[(size_t)c.layer]->mixer().cache_spec();
+        const CacheSpec s = blocks_[(size_t)c.layer]->cache_spec();
         if (seen[(size_t)c.cache] && specs[(size_t)c.cache] != s)
             throw ConfigError("cache entry " + std::to_string(c.cache) + " is used by layers with different needs");
         specs[(size_t)c.cache] = s;
         seen[(size_t)c.cache] = 1;
     }
+    if (spec_.embedding_cache >= 0) specs[(size_t)spec_.embedding_cache] = embedding_->cache_spec();
     return specs;
 }
 
@@ -103,6 +111,7 @@ size_t Model::weight_bytes() const {
         Block& b = *blocks_[(size_t)c.layer];
         total += b.mixer().weight_bytes() + b.feed_forward().weight_bytes();
         for (auto& kv : b.norms()) total += kv.second->weight_bytes();
+        for (auto& kv : b.wraps()) total += kv.second->weight_bytes();
         if (c.remix >= 0) total += remixes_[(size_t)c.remix]->weight_bytes();
     }
     return total;
@@ -111,8 +120,15 @@ size_t Model::weight_bytes() const {
 Tensor Model::forward(StepContext& ctx) {
     Workspace& ws = *ctx.workspace;
     ctx.position = position_.get();
+    ctx.embedding_cache = spec_.embedding_cache;
     Tensor x = ws.get("stream", ctx.n_tokens, spec_.width, DType::F32);
     embedding_->forward(ctx, x);
+    const Tensor one_stream = x;
+    if (spec_.streams > 1) {
+        // the embedding's output enters every copy of the stream; the blocks work on all of them side by side
+        x = ws.get("streams", ctx.n_tokens, spec_.width * spec_.streams, DType::F32);
+        ops::streams_spread(ctx.launch, one_stream, x, spec_.streams);
+    }
     Tensor x0;
     if (!remixes_.empty()) {
         // the embedding's output stays at hand for the stream mixes
@@ -123,6 +139,13 @@ Tensor Model::forward(StepContext& ctx) {
     for (const LayerCall& c : spec_.schedule) {
         if (c.remix >= 0) remixes_[(size_t)c.remix]->forward(ctx, x, x0);
         blocks_[(size_t)c.layer]->forward(ctx, x, c);
+    }
+    if (spec_.streams > 1) {
+        ops::StreamsStep sum;                 // the final norm reads the sum of the copies
+        Tensor total = one_stream;
+        sum.sum_out = &total;
+        ops::streams_step(ctx.launch, x, spec_.streams, sum);
+        x = one_stream;
     }
     Tensor logits = ws.get("logits", ctx.n_rows, spec_.vocab_size, DType::F32);
     if (ctx.n_rows) {

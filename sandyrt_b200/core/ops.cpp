@@ -485,6 +485,9 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     const float cap = extras ? extras->softcap : 0.0f;
     const int chunk = extras ? extras->chunk : 0;
     if (cap < 0.0f || chunk < 0) throw UnsupportedShape("attention: softcap and chunk must not be negative");
+    const float* db = extras ? extras->dist_bias : nullptr;
+    const int n_dist = extras ? extras->n_dist : 0;
+    if (db && n_dist < 1) throw UnsupportedShape("attention: a bias by distance needs at least one row");
     const bool ruled = cap > 0.0f || chunk > 0;           // only kernels with a form for these rules take such steps
     const int d = c.head_dim, hkv = c.n_kv_heads;
     if (d % 16 != 0 || d > kMaxHeadDim) throw UnsupportedShape("attention: head size " + std::to_string(d) + " must be a multiple of 16, at most " + std::to_string(kMaxHeadDim));
@@ -497,7 +500,7 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     const double attn_bytes = 2.0 * s.kv_tokens * hkv * d * q.elem_size() + 2 * tensor_bytes(&q);
     const double attn_flops = 4.0 * s.pairs * n_heads * d;
     const std::string shape = "(H=" + std::to_string(n_heads) + ",Hkv=" + std::to_string(hkv) + ",D=" + std::to_string(d) + ")";
-    if (s.max_q_len > 1 && q.dtype == DType::BF16 && d <= 128) {
+    if (!db && s.max_q_len > 1 && q.dtype == DType::BF16 && d <= 128) {
         static const bool use_tc = env_int("SANDYRT_PREFILL_TC", 1) != 0;     // 0 keeps every head size on the mma.sync kernel
         if (use_tc && d == 64) {
             static auto fn = SANDY_KERNEL(attention_prefill_tc, sandy_prefill_attention_tc_cap);
@@ -524,7 +527,7 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     // 8 x 392: 9.4 / 8.7; 8 tokens x 24 heads x 392: 11.3 / 16.6; 8 x 12 x 2,000: 13.2 / 36.2.
     // Steps with capped scores or chunks of positions: this kernel is the decode kernel that has a form for them, so it
     // takes them all (with few keys it is one launch of one split); a chunk bounds the keys a query walks.
-    if (s.max_q_len == 1 && q.dtype == DType::BF16 && d <= 128 && T <= 65535 &&
+    if (!db && s.max_q_len == 1 && q.dtype == DType::BF16 && d <= 128 && T <= 65535 &&
         (ruled || (n_heads / hkv >= kSharedKvMinHeads && (int64_t)T * n_heads * s.max_blocks * c.page_size >= kSharedKvMinTriples))) {
         const int max_kv = chunk > 0 ? std::min(chunk, s.max_blocks * c.page_size) : s.max_blocks * c.page_size;
         const int tiles = hkv * ((n_heads / hkv + 15) / 16), groups = (max_kv + 15) / 16;
@@ -540,7 +543,7 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
               "decode_attention_shared" + shape);
         return;
     }
-    if (!ruled && s.max_q_len == 1 && decode_head_dim(q.dtype, d)) {
+    if (!db && !ruled && s.max_q_len == 1 && decode_head_dim(q.dtype, d)) {
         const int max_kv = s.max_blocks * c.page_size;
         const int splits = std::min(decode_splits(T, n_heads, max_kv), kClusterMaxSplits);
         const size_t stage = 2 * (size_t)c.page_size * (size_t)d * q.elem_size();
@@ -589,11 +592,11 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
         }
         return;
     }
-    static auto fn = SANDY_KERNEL(attention, sandy_paged_attention_cap);
+    static auto fn = SANDY_KERNEL(attention, sandy_paged_attention_bias);
     OpTimer timer(l, "attention, general", attn_bytes, attn_flops);
     check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.token_seq, s.positions, out.data,
-             (int)out.ld, T, n_heads, hkv, d, c.page_size, scale, window, cap, chunk, c.num_pages, code_of(q.dtype), sk, og,
-             l.kernel_status, l.stream),
+             (int)out.ld, T, n_heads, hkv, d, c.page_size, scale, window, cap, chunk, c.num_pages, code_of(q.dtype), sk, og, db,
+             n_dist, l.kernel_status, l.stream),
           "paged_attention" + shape);
 }
 
@@ -794,6 +797,22 @@ void moe_route_scored(const Launch& l, const Tensor& logits, const Tensor* corre
     check(group(r.expert_of, r.n_tokens * r.top, r.n_experts, r.group_start, r.entry_of_slot, r.slot_of_entry, l.stream), "moe_group");
 }
 
+void moe_route_softmax(const Launch& l, const Tensor& logits, const Tensor* correction, const SoftmaxRoute& rule, const Routing& r) {
+    if (logits.dtype != DType::F32 || logits.rows != r.n_tokens || logits.cols != r.n_experts ||
+        (correction && (correction->dtype != DType::F32 || correction->numel() != r.n_experts)))
+        throw KernelError("moe_route_softmax: float32 logits [tokens, experts] and a float32 correction [experts] expected");
+    static auto route = SANDY_KERNEL(moe, sandy_moe_route_softmax);
+    static auto group = SANDY_KERNEL(moe, sandy_moe_group);
+    {
+        OpTimer timer(l, "expert routing", tensor_bytes(&logits), 0);
+        check(route((const float*)logits.data, (int)logits.ld, correction ? (const float*)correction->data : nullptr, r.n_tokens,
+                    r.n_experts, r.top, rule.weight_scale, rule.norm_eps, rule.renormalize ? 1 : 0, r.expert_of, r.weight_of, l.stream),
+              "moe_route_softmax(E=" + std::to_string(r.n_experts) + ",top=" + std::to_string(r.top) + ")");
+    }
+    OpTimer timer(l, "expert grouping", 12.0 * r.n_tokens * r.top, 0);
+    check(group(r.expert_of, r.n_tokens * r.top, r.n_experts, r.group_start, r.entry_of_slot, r.slot_of_entry, l.stream), "moe_group");
+}
+
 void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gather, const Tensor& w, ExpertAct act, Tensor& out,
                     Tensor* sorted) {
     if (r.n_experts <= 0 || w.rows % r.n_experts) throw KernelError("expert_product: the weight's rows do not divide into the experts");
@@ -845,17 +864,29 @@ void moe_combine(const Launch& l, const Routing& r, const Tensor& rows, Tensor& 
           "moe_combine");
 }
 
+void moe_combine_identity(const Launch& l, const Routing& r, int n_real, const Tensor& h, const Tensor& rows, Tensor& y, bool add) {
+    if (rows.dtype != DType::F32 || y.dtype != DType::F32 || rows.rows != (int64_t)r.n_tokens * r.top || y.rows != r.n_tokens ||
+        rows.cols != y.cols || h.rows != y.rows || h.cols != y.cols || (h.dtype != DType::F32 && h.dtype != DType::BF16))
+        throw KernelError("moe_combine_identity: float32 rows [tokens * top, width], y and h [tokens, width] expected");
+    static auto fn = SANDY_KERNEL(moe, sandy_moe_combine_identity);
+    OpTimer timer(l, "expert combine", tensor_bytes(&rows) + (add ? 2.0 : 1.0) * tensor_bytes(&y) + tensor_bytes(&h), 0);
+    check(fn((const float*)rows.data, (int)rows.ld, r.weight_of, r.slot_of_entry, r.expert_of, n_real, h.data, (int)h.ld,
+             code_of(h.dtype), r.n_tokens, r.top, (float*)y.data, (int)y.ld, (int)y.cols, add ? 1 : 0, l.stream),
+          "moe_combine_identity");
+}
+
 void attention_prepare(const Launch& l, const AttentionPrepare& p, const Tensor& proj, const KVView& c, const int* block_table,
                        int max_blocks, const int* token_seq, const int* positions, Tensor& q_out) {
     if (proj.dtype != c.dtype || q_out.dtype != proj.dtype || q_out.rows != proj.rows || q_out.cols != (int64_t)p.n_heads * c.head_dim ||
         c.n_kv_heads != p.n_kv_heads || c.head_dim < p.qk_dim || c.head_dim < p.v_dim)
         throw KernelError("attention_prepare: the projection, the queries and the cache disagree");
-    static auto fn = SANDY_KERNEL(attention_prepare, sandy_attention_prepare_ext);
+    static auto fn = SANDY_KERNEL(attention_prepare, sandy_attention_prepare_pos);
     OpTimer timer(l, "q/k norm + rotary + cache write", 2.0 * tensor_bytes(&proj), 0);
     check(fn(proj.data, (int)proj.ld, p.q_off, p.k_off, p.v_off, (int)proj.rows, p.n_heads, p.n_kv_heads, p.qk_dim, p.v_dim,
              c.head_dim, p.q_gain, p.k_gain, p.eps, p.freq, p.rot_dims, positions, token_seq, block_table, max_blocks, c.k, c.v,
              c.page_stride, c.page_size, c.num_pages, p.write_cache ? 1 : 0, q_out.data, (int)q_out.ld, p.gate_in, p.ld_gate,
-             p.gate_out, p.gate_scale, p.q_head_scale, p.v_unit_eps, code_of(proj.dtype), l.kernel_status, l.stream),
+             p.gate_out, p.gate_scale, p.q_head_scale, p.v_unit_eps, p.per_head_norm ? 1 : 0, p.q_pos_coef, p.q_pos_every,
+             code_of(proj.dtype), l.kernel_status, l.stream),
           "attention_prepare");
 }
 
@@ -889,6 +920,135 @@ void conv_tail(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Te
              s.q_start, s.seq_slots, s.n_seqs, l.stream),
           "conv_tail");
 }
+
+void conv_tail(const Launch& l, const StepSeqs& s, const Tensor& rows, int n_taps, const StateView& state, int64_t tail_off) {
+    if (state.dtype != DType::F32 || n_taps < 1 || tail_off < 0 || tail_off + (int64_t)(n_taps - 1) * rows.cols > state.row_elems)
+        throw KernelError("conv_tail: the tail does not fit the float32 state");
+    if (n_taps == 1) return;
+    static auto fn = SANDY_KERNEL(matrix_state, sandy_conv_tail);
+    OpTimer timer(l, "conv tail", 0, 0);
+    check(fn(rows.data, (int)rows.ld, code_of(rows.dtype), (int)rows.cols, n_taps, (float*)state.data, state.row_elems, tail_off,
+             s.q_start, s.seq_slots, s.n_seqs, l.stream),
+          "conv_tail");
+}
+
+// ---- selective state-space mixer -----------------------------------------------------------------------------
+int64_t ssm_state_floats(const SsmShape& m) { return (int64_t)m.n_heads * m.v_dim * m.state; }
+
+void ssm_prepare(const Launch& l, const StepSeqs& s, const SsmShape& m, const Tensor& proj, const Tensor& taps, const Tensor* conv_bias,
+                 const Tensor& dt_raw, const float* dt_bias, const float* a_log, const StateView& state, int64_t tail_off,
+                 Tensor& xbc, Tensor& dta) {
+    const int64_t channels = (int64_t)m.n_heads * m.v_dim + 2 * (int64_t)m.n_groups * m.state;
+    if (proj.cols != channels || proj.rows != s.n_tokens || taps.dtype != DType::F32 || taps.numel() != channels * m.n_taps ||
+        (conv_bias && (conv_bias->dtype != DType::F32 || conv_bias->numel() != channels)) || dt_raw.dtype != DType::F32 ||
+        dt_raw.cols != m.n_heads || dt_raw.rows != proj.rows || xbc.dtype != DType::F32 || xbc.cols != channels ||
+        xbc.rows != proj.rows || dta.dtype != DType::F32 || dta.cols != 2 * m.n_heads || !dta.contiguous() ||
+        state.dtype != DType::F32 || tail_off + (int64_t)(m.n_taps - 1) * channels > state.row_elems)
+        throw KernelError("ssm_prepare: shapes disagree");
+    static auto fn = SANDY_KERNEL(ssm_state, sandy_ssm_prepare);
+    OpTimer timer(l, "state space: conv + gates", tensor_bytes(&proj) + tensor_bytes(&xbc), 0);
+    check(fn(proj.data, (int)proj.ld, code_of(proj.dtype), (int)channels, (const float*)taps.data, m.n_taps,
+             conv_bias ? (const float*)conv_bias->data : nullptr, (const float*)dt_raw.data, (int)dt_raw.ld, dt_bias, a_log, m.n_heads,
+             (const float*)state.data, state.row_elems, tail_off, s.token_seq, s.q_start, s.seq_slots, (float*)xbc.data, (int)xbc.ld,
+             (float*)dta.data, s.n_tokens, l.stream),
+          "ssm_prepare");
+}
+
+void ssm_scan(const Launch& l, const StepSeqs& s, const SsmShape& m, const Tensor& xbc, const Tensor& dta, const float* d_skip,
+              const StateView& state, Tensor& out) {
+    if (out.dtype != DType::F32 || out.cols != (int64_t)m.n_heads * m.v_dim || xbc.dtype != DType::F32 || dta.dtype != DType::F32 ||
+        !dta.contiguous() || state.dtype != DType::F32 || ssm_state_floats(m) > state.row_elems)
+        throw KernelError("ssm_scan: float32 xbc, dta, out [T, H * P] and a float32 state of H * P * N floats expected");
+    static auto fn = SANDY_KERNEL(ssm_state, sandy_ssm_scan);
+    const double st = 2.0 * s.n_seqs * (double)ssm_state_floats(m) * 4.0;
+    OpTimer timer(l, "state space: recurrence", st + tensor_bytes(&xbc) + tensor_bytes(&out), 6.0 * s.n_tokens * (double)ssm_state_floats(m));
+    check(fn((const float*)xbc.data, (int)xbc.ld, (const float*)dta.data, d_skip, (float*)state.data, state.row_elems, s.q_start,
+             s.seq_slots, (float*)out.data, (int)out.ld, s.n_seqs, m.n_heads, m.n_groups, m.state, m.v_dim, l.stream),
+          "ssm_scan(H=" + std::to_string(m.n_heads) + ",N=" + std::to_string(m.state) + ",P=" + std::to_string(m.v_dim) + ")");
+}
+
+void gated_group_norm(const Launch& l, const Tensor& y, const Tensor& z, const Tensor* gain, float eps, int groups, Tensor& out) {
+    if (y.dtype != DType::F32 || z.rows != y.rows || z.cols != y.cols || out.rows != y.rows || out.cols != y.cols || out.dtype != z.dtype ||
+        groups < 1 || y.cols % groups || (gain && (gain->dtype != DType::F32 || gain->numel() != y.cols)))
+        throw KernelError("gated_group_norm: float32 y, z and out [T, cols] of one type, float32 gain [cols] expected");
+    static auto fn = SANDY_KERNEL(ssm_state, sandy_gated_group_norm);
+    OpTimer timer(l, "gate + group norm", tensor_bytes(&y) + tensor_bytes(&z) + tensor_bytes(&out), 0);
+    check(fn((const float*)y.data, (int)y.ld, z.data, (int)z.ld, gain ? (const float*)gain->data : nullptr, eps, groups, out.data,
+             (int)out.ld, (int)y.rows, (int)y.cols, code_of(out.dtype), l.stream),
+          "gated_group_norm");
+}
+
+// ---- a residual stream in several copies ----------------------------------------------------------------------
+int streams_max() {
+    static auto fn = SANDY_KERNEL(streams, sandy_streams_max);
+    return fn();
+}
+
+void streams_step(const Launch& l, Tensor& X, int n_streams, const StreamsStep& p) {
+    if (X.dtype != DType::F32 || n_streams < 1 || X.cols % n_streams) throw KernelError("streams_step: float32 streams [T, S * width] expected");
+    const int64_t W = X.cols / n_streams;
+    auto f32 = [](const Tensor* t, int64_t n) { return t && t->dtype == DType::F32 && t->numel() == n; };
+    if (p.y && (p.y->dtype != DType::F32 || p.y->rows != X.rows || p.y->cols != W || !p.gate || p.gate->dtype != DType::F32 ||
+                p.gate->rows != X.rows || p.gate->cols != W || !f32(p.gate_bias, W) || !f32(p.mix, (int64_t)n_streams * n_streams) ||
+                !f32(p.out_w, n_streams)))
+        throw KernelError("streams_step: the write needs float32 y and gate [T, width], gate_bias [width], mix [S, S] and out [S]");
+    if (p.in_w && (!f32(p.in_w, n_streams) || !f32(p.gain, W) || !p.h || p.h->rows != X.rows || p.h->cols != W))
+        throw KernelError("streams_step: the read needs float32 in [S] and gain [width] and h [T, width]");
+    if (p.sum_out && (p.sum_out->dtype != DType::F32 || p.sum_out->rows != X.rows || p.sum_out->cols != W))
+        throw KernelError("streams_step: the sum is float32 [T, width]");
+    if (left_out("layernorm")) return;
+    static auto fn = SANDY_KERNEL(streams, sandy_streams_step);
+    OpTimer timer(l, "streams: write + norm", (p.y ? 2.0 : 1.0) * tensor_bytes(&X) + 2 * tensor_bytes(p.y) + tensor_bytes(p.h) + tensor_bytes(p.sum_out), 0);
+    check(fn((float*)X.data, (int)X.ld, (int)X.rows, n_streams, (int)W, p.y ? (const float*)p.y->data : nullptr, p.y ? (int)p.y->ld : 0,
+             p.y ? (const float*)p.gate->data : nullptr, p.y ? (int)p.gate->ld : 0, p.y ? (const float*)p.gate_bias->data : nullptr,
+             p.y ? (const float*)p.mix->data : nullptr, p.y ? (const float*)p.out_w->data : nullptr,
+             p.in_w ? (const float*)p.in_w->data : nullptr, p.in_w ? (const float*)p.gain->data : nullptr, p.eps,
+             p.in_w ? p.h->data : nullptr, p.in_w ? (int)p.h->ld : 0, p.in_w ? code_of(p.h->dtype) : 0,
+             p.sum_out ? (float*)p.sum_out->data : nullptr, p.sum_out ? (int)p.sum_out->ld : 0, l.stream),
+          "streams_step(S=" + std::to_string(n_streams) + ",width=" + std::to_string(W) + ")");
+}
+
+void streams_spread(const Launch& l, const Tensor& x, Tensor& X, int n_streams) {
+    if (x.dtype != DType::F32 || X.dtype != DType::F32 || X.rows != x.rows || X.cols != x.cols * n_streams)
+        throw KernelError("streams_spread: float32 x [T, width] and X [T, S * width] expected");
+    static auto fn = SANDY_KERNEL(streams, sandy_streams_spread);
+    OpTimer timer(l, "streams: spread", tensor_bytes(&x) + tensor_bytes(&X), 0);
+    check(fn((const float*)x.data, (int)x.ld, (float*)X.data, (int)X.ld, (int)x.rows, n_streams, (int)x.cols, l.stream), "streams_spread");
+}
+
+void canon_conv(const Launch& l, const StepSeqs& s, const Tensor& h, const Tensor& taps, int n_taps, const StateView& state,
+                int64_t tail_off, Tensor& c) {
+    if (h.dtype != c.dtype || h.rows != c.rows || h.cols != c.cols || h.rows != s.n_tokens || taps.dtype != DType::F32 ||
+        taps.numel() != h.cols * n_taps || state.dtype != DType::F32 || tail_off + (int64_t)(n_taps - 1) * h.cols > state.row_elems)
+        throw KernelError("canon_conv: h and c [T, width] of one type, float32 taps [width, n_taps] and a float32 state expected");
+    static auto fn = SANDY_KERNEL(streams, sandy_canon_conv);
+    OpTimer timer(l, "input conv", tensor_bytes(&h) + tensor_bytes(&c), 0);
+    check(fn(h.data, (int)h.ld, (const float*)taps.data, n_taps, (const float*)state.data, state.row_elems, tail_off, s.token_seq,
+             s.q_start, s.seq_slots, c.data, (int)c.ld, (int)h.rows, (int)h.cols, code_of(h.dtype), l.stream),
+          "canon_conv");
+}
+
+void embed_bigram(const Launch& l, const StepSeqs& s, const int* ids, const int* positions, const Tensor& wte, const Tensor& bigram,
+                  const Tensor* wpe, const BigramEmbed& b, const StateView& state, Tensor& x, int max_q_len) {
+    if (x.dtype != DType::F32 || x.cols != wte.cols || bigram.dtype != wte.dtype || bigram.cols != wte.cols || bigram.rows != b.buckets + 1 ||
+        (wpe && (wpe->dtype != wte.dtype || wpe->cols != wte.cols)) || state.dtype != DType::I32 || state.row_elems < 1 ||
+        !wte.contiguous() || !bigram.contiguous() || (wpe && !wpe->contiguous()))
+        throw KernelError("embed_bigram: tables of one type and width, bigram [buckets + 1, width], a float32 x and an int32 state expected");
+    static auto fn = SANDY_KERNEL(streams, sandy_embed_bigram);
+    static auto keep = SANDY_KERNEL(streams, sandy_bigram_keep);
+    {
+        OpTimer timer(l, "embedding", (double)s.n_tokens * x.cols * (3.0 * wte.elem_size() + 4.0), 0);
+        check(fn(ids, positions, s.token_seq, s.q_start, s.seq_slots, wte.data, bigram.data, wpe ? wpe->data : nullptr, b.buckets,
+                 b.mul_prev, b.mul_cur, (int*)state.data, state.row_elems, (float*)x.data, (int)x.ld, s.n_tokens, (int)wte.rows,
+                 wpe ? (int)wpe->rows : 0, (int)x.cols, code_of(wte.dtype), max_q_len <= 1 ? 1 : 0, l.status, l.stream),
+              "embed_bigram");
+    }
+    if (max_q_len > 1) {
+        OpTimer timer(l, "embedding: last tokens kept", 0, 0);
+        check(keep(ids, s.q_start, s.seq_slots, (int*)state.data, state.row_elems, s.n_seqs, l.stream), "bigram_keep");
+    }
+}
+
 
 void delta_scan(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Tensor& qkv, const Tensor& bg, const StateView& state,
                 Tensor& out, int max_q_len) {

@@ -138,6 +138,10 @@ struct AttentionExtras {
     const float* out_gate = nullptr;
     float softcap = 0.0f;
     int chunk = 0;
+    // A learned bias by distance: row min(i - j, n_dist - 1) of dist_bias (float32 [n_dist, H]) joins the score of query i
+    // and key j after the scale and the cap.  Null: none.
+    const float* dist_bias = nullptr;
+    int n_dist = 0;
 };
 // The widest head any attention kernel takes (the general kernel; the tensor-core prompt kernels take up to 128, the
 // decode kernels 16 / 32 / 64 / 128 and, in bfloat16, 256).
@@ -232,6 +236,13 @@ struct ScoredRoute {
     float weight_scale = 1.0f, norm_eps = 0.0f;
 };
 void moe_route_scored(const Launch& l, const Tensor& logits, const Tensor* correction, const ScoredRoute& rule, const Routing& r);
+// Routing by softmax scores: s = softmax over all experts' logits; the choice is by s + correction; the weights are the
+// chosen s themselves times weight_scale, over their sum (+ norm_eps) only with `renormalize`.
+struct SoftmaxRoute {
+    float weight_scale = 1.0f, norm_eps = 0.0f;
+    bool renormalize = false;
+};
+void moe_route_softmax(const Launch& l, const Tensor& logits, const Tensor* correction, const SoftmaxRoute& rule, const Routing& r);
 enum class ExpertAct : int { None = 0, ReluSquared = 1 };
 // out[s] = act(W_e a[row(s)]) for the slots s of every expert e; w [E * N, K]; with `gather` a slot reads its token's
 // row of `a` ([T, K]), else row s ([T * top, K]).  out [T * top, N].
@@ -246,6 +257,9 @@ void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gat
                     Tensor* sorted = nullptr);
 // y[t] (+)= sum_j weight[t, j] * rows[slot of (t, j)]; rows float32 [T * top, width], y float32 [T, width].
 void moe_combine(const Launch& l, const Routing& r, const Tensor& rows, Tensor& y, bool add);
+// The same where the experts from n_real on have no matrices and hand their input on: such an entry contributes
+// weight * h[t] (h [T, width], the feed-forward's input) instead of a computed row.
+void moe_combine_identity(const Launch& l, const Routing& r, int n_real, const Tensor& h, const Tensor& rows, Tensor& y, bool add);
 
 // ---- between a q/k/v projection and attention (attention_prepare.cu) -----------------------------------------
 struct AttentionPrepare {
@@ -262,6 +276,10 @@ struct AttentionPrepare {
     float gate_scale = 1.0f;
     const float* q_head_scale = nullptr;                           // float32 [H]: a factor on each query head, or null
     float v_unit_eps = 0.0f;                                       // > 0: every value head over its root mean square (this eps)
+    bool per_head_norm = false;                                    // every query and key head over its own root mean square (eps);
+                                                                   // the gains may then be null
+    float q_pos_coef = 0.0f;                                       // with q_pos_every > 0 the query at position p is multiplied by
+    int q_pos_every = 0;                                           // 1 + q_pos_coef * ln(floor((p + 1) / q_pos_every) + 1)
     bool write_cache = true;
 };
 void attention_prepare(const Launch& l, const AttentionPrepare& p, const Tensor& proj, const KVView& cache,
@@ -292,6 +310,55 @@ struct MlstmShape { int n_heads = 0, qk_dim = 0, v_dim = 0, q_off = 0, k_off = 0
 // gates float32 [T, >= 2H]: input-gate pre-activations, then forget-gate ones; gate_bias float32 [2H].
 void mlstm_scan(const Launch& l, const StepSeqs& s, const MlstmShape& m, const Tensor& proj, const Tensor& gates,
                 const float* gate_bias, const StateView& state, Tensor& out, int max_q_len);
+
+// The last n_taps - 1 rows of `rows` ([T, channels], any pitch) of every request into its state at tail_off, as the
+// convolutions above keep theirs (rows before the step come from the old tail).
+void conv_tail(const Launch& l, const StepSeqs& s, const Tensor& rows, int n_taps, const StateView& state, int64_t tail_off);
+
+// ---- a selective state-space mixer with one decay per head (ssm_state.cu) ----------------------------------------
+struct SsmShape { int n_heads = 0, n_groups = 0, state = 0, v_dim = 0, n_taps = 0; };
+int64_t ssm_state_floats(const SsmShape& m);                       // S [H][P][N]; the convolution's tail follows it
+// proj: the x, B and C channels ([T, H * P + 2 G * N], a column range of the input projection); taps float32 [channels,
+// n_taps], conv_bias float32 [channels] or null; dt_raw float32 [T, H]; xbc float32 [T, channels] = silu(conv + bias);
+// dta float32 [T, 2H]: dt = softplus(raw + dt_bias), then -exp(a_log) dt.
+void ssm_prepare(const Launch& l, const StepSeqs& s, const SsmShape& m, const Tensor& proj, const Tensor& taps, const Tensor* conv_bias,
+                 const Tensor& dt_raw, const float* dt_bias, const float* a_log, const StateView& state, int64_t tail_off,
+                 Tensor& xbc, Tensor& dta);
+// S <- exp(dta[1]) S + dt B x^T; out = S^T C + d_skip x, float32 [T, H * P]; d_skip float32 [H] or null.
+void ssm_scan(const Launch& l, const StepSeqs& s, const SsmShape& m, const Tensor& xbc, const Tensor& dta, const float* d_skip,
+              const StateView& state, Tensor& out);
+// out = (y * silu(z)) over its root mean square in `groups` equal parts of a row (eps inside the root), times gain.
+void gated_group_norm(const Launch& l, const Tensor& y, const Tensor& z, const Tensor* gain, float eps, int groups, Tensor& out);
+
+// ---- a residual stream in several copies (streams.cu) -------------------------------------------------------------
+// What one pass over the streams X (float32 [T, S * width]) does, each part optional and in this order:
+//   write   X_t <- sum_s mix[s, t] X_s + out_w[t] * y * sigmoid(gate + gate_bias)     (y, gate float32 [T, width])
+//   sum     sum_out = sum_s X_s                                                        (float32 [T, width])
+//   read    h = LayerNorm(sum_s in_w[s] X_s) * gain, no offset                         (h [T, width] of the compute type)
+struct StreamsStep {
+    const Tensor* y = nullptr;
+    const Tensor* gate = nullptr;
+    const Tensor* gate_bias = nullptr;       // float32 [width]
+    const Tensor* mix = nullptr;             // float32 [S, S], indexed [from, to]
+    const Tensor* out_w = nullptr;           // float32 [S]
+    const Tensor* in_w = nullptr;            // float32 [S]
+    const Tensor* gain = nullptr;            // float32 [width]
+    float eps = 0.0f;
+    Tensor* h = nullptr;
+    Tensor* sum_out = nullptr;
+};
+int streams_max();
+void streams_step(const Launch& l, Tensor& X, int n_streams, const StreamsStep& step);
+void streams_spread(const Launch& l, const Tensor& x, Tensor& X, int n_streams);
+// c = h + conv(h): a short causal convolution over time on every channel (taps float32 [width, n_taps], the last column
+// the token's own), rows before the step from the request's tail at tail_off of its state.
+void canon_conv(const Launch& l, const StepSeqs& s, const Tensor& h, const Tensor& taps, int n_taps, const StateView& state,
+                int64_t tail_off, Tensor& c);
+// x[t] = wte[id] + bigram[(id_before * mul_prev + id * mul_cur) mod buckets] + wpe[pos]; a request's first token reads
+// row `buckets`; the token before a step's first one is the int32 state of the request, which then takes the step's last.
+struct BigramEmbed { int buckets = 0; long long mul_prev = 0, mul_cur = 0; };
+void embed_bigram(const Launch& l, const StepSeqs& s, const int* ids, const int* positions, const Tensor& wte, const Tensor& bigram,
+                  const Tensor* wpe, const BigramEmbed& b, const StateView& state, Tensor& x, int max_q_len);
 
 // Choose one token per row of float32 `logits`; per-row option arrays may be null.  With `feedback`
 // the drawn token also replaces the row's input token, its position moves on, and the token is

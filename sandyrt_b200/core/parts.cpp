@@ -25,16 +25,17 @@ ops::AttentionStep StepContext::attention_step(int group) const {
 
 // ---- NormedInput ---------------------------------------------------------------------------------------
 const Tensor& NormedInput::tensor() {
-    if (!tensor_.defined()) {
+    if (!fixed_ && !tensor_.defined()) {
         tensor_ = ctx_.workspace->get("normed", x_.rows, x_.cols, ctx_.compute_dtype);
-        norm_.forward(ctx_, x_, tensor_, nullptr, (int)x_.rows);
+        norm_->forward(ctx_, x_, tensor_, nullptr, (int)x_.rows);
     }
     return tensor_;
 }
 
 bool NormedInput::fusable(ops::FusedNorm& out) const {
+    if (fixed_) return false;
     LayerNormParams p;
-    if (!norm_.layernorm_params(p)) return false;
+    if (!norm_->layernorm_params(p)) return false;
     out.x = x_;
     out.gamma = p.gamma;
     out.beta = p.beta;
@@ -43,7 +44,7 @@ bool NormedInput::fusable(ops::FusedNorm& out) const {
 }
 
 bool NormedInput::rms(RmsNormParams& out) const {
-    if (!norm_.rms_params(out)) return false;
+    if (fixed_ || !norm_->rms_params(out)) return false;
     out.x = x_;
     return true;
 }
@@ -403,7 +404,7 @@ Table& table() {
     static Table t;
     static std::once_flag once;
     std::call_once(once, [] {
-        for (const char* fam : {"mixer", "feed_forward", "norm", "position", "embedding", "head", "remix", "block"}) t[fam];
+        for (const char* fam : {"mixer", "feed_forward", "norm", "position", "embedding", "head", "remix", "wrap", "block"}) t[fam];
         t["norm"]["layernorm"] = simple<LayerNorm>();
         t["position"]["learned_absolute"] = simple<LearnedAbsolute>();
         t["position"]["none"] = simple<NoPosition>();
@@ -427,6 +428,7 @@ Table& table() {
             register_hybrid_parts();
             register_latent_parts();
             register_capped_parts();
+            register_stream_parts();
         });
         entered = false;
     }
@@ -440,7 +442,7 @@ void register_part(const std::string& family, const std::string& kind, PartFacto
     Table& t = table();
     std::lock_guard<std::mutex> g(table_lock());
     auto it = t.find(family);
-    if (it == t.end()) throw ConfigError("unknown part family '" + family + "'; one of mixer, feed_forward, norm, position, embedding, head, remix, block");
+    if (it == t.end()) throw ConfigError("unknown part family '" + family + "'; one of mixer, feed_forward, norm, position, embedding, head, remix, wrap, block");
     it->second[kind] = std::move(factory);
 }
 

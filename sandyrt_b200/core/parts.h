@@ -18,6 +18,8 @@
 //   FeedForward       forward(ctx, h, x)                       x += ff(h), in place
 //   Block             forward(ctx, x, call)                    runs its norms, mixer, feed-forward
 //   Remix             forward(ctx, x, x0)                      x <- f(x, x0), x0 the embedding's output
+//   Wrap              read(ctx, X, ..) / write(ctx, X, ..)     how a sublayer reads the stream(s) and how its result joins
+//                                                              them, for blocks whose sublayers do more than x += f(norm(x))
 //
 // `x` is the residual stream: float32 [tokens, width] in both compute dtypes, so the residual sum is
 // always formed and kept in 32-bit.  `h` is a normed copy in the compute dtype, handed over as a
@@ -62,6 +64,7 @@ struct StepContext {
     Workspace* workspace = nullptr;
     DeviceCaches* caches = nullptr;
     PositionEncoding* position = nullptr;    // the model's position encoding
+    int embedding_cache = -1;                // the cache entry of the embedding's own state per request, or -1
     // Set by a block that norms a sublayer's output before it joins the stream: a mixer or feed-forward that
     // says `can_overwrite()` then writes its result over the tensor it is given instead of adding to it.
     bool overwrite = false;
@@ -125,6 +128,9 @@ class Embedding : public Part {
 public:
     using Part::Part;
     virtual const Tensor* table() const { return nullptr; }
+    // A fixed-size state per request (something of the tokens before, kept between steps); the model's description
+    // names the cache entry (ModelSpec::embedding_cache), the step hands it over as StepContext::embedding_cache.
+    virtual CacheSpec cache_spec() const { return CacheSpec::none(); }
     virtual void forward(StepContext& ctx, Tensor& x) = 0;
 };
 
@@ -139,7 +145,9 @@ public:
 // A normed view of the residual stream that has not been computed yet.
 class NormedInput {
 public:
-    NormedInput(StepContext& ctx, Norm& norm, const Tensor& x) : ctx_(ctx), norm_(norm), x_(x) {}
+    NormedInput(StepContext& ctx, Norm& norm, const Tensor& x) : ctx_(ctx), norm_(&norm), x_(x) {}
+    // An input a block has computed already (a norm with something behind it): consumers get the tensor as it is.
+    NormedInput(StepContext& ctx, const Tensor& computed) : ctx_(ctx), x_(computed), tensor_(computed), fixed_(true) {}
     int64_t rows() const { return x_.rows; }
     int64_t cols() const { return x_.cols; }
     const Tensor& tensor();                            // computed once and shared
@@ -147,9 +155,10 @@ public:
     bool rms(RmsNormParams& out) const;                // the stream's rows and the norm's parameters, if it is an RMS norm
 private:
     StepContext& ctx_;
-    Norm& norm_;
+    Norm* norm_ = nullptr;
     Tensor x_;
     Tensor tensor_;
+    bool fixed_ = false;
 };
 
 class Mixer : public Part {
@@ -175,6 +184,25 @@ public:
     virtual void forward(StepContext& ctx, Tensor& x, const Tensor& x0) = 0;
 };
 
+// What a block puts around one sublayer when that is more than x += f(norm(x)): how the sublayer's input is read from
+// the stream(s) X (float32 [tokens, streams * width]) and how its result joins them.
+class Wrap : public Part {
+public:
+    using Part::Part;
+    // float32 numbers per request that the wrap keeps between steps (the block adds them to its layer's cache entry
+    // and hands their place over as `state` and `offset`)
+    virtual int64_t state_floats() const { return 0; }
+    // What `read` hands back: `sublayer_in` is what the sublayer reads; `gate` whatever `write` needs again.
+    struct Input { Tensor sublayer_in; Tensor gate; };
+    // Reads the stream for this wrap's sublayer.  `before` / `before_y` / `before_in`: another wrap of the same block
+    // whose write is still owed (its sublayer's result and what its read handed back); the read then does that write
+    // first, in the same pass over the streams.
+    virtual Input read(StepContext& ctx, Tensor& X, const StateView* state, int64_t offset, Wrap* before, const Tensor* before_y,
+                       const Input* before_in) = 0;
+    // X <- the streams with the sublayer's result y (float32 [tokens, width]) joined.
+    virtual void write(StepContext& ctx, Tensor& X, const Tensor& y, const Input& in) = 0;
+};
+
 // An arrangement of norms, a mixer and a feed-forward (built from a LayerSpec).
 class Block {
 public:
@@ -183,13 +211,17 @@ public:
         : mixer_(std::move(mixer)), ff_(std::move(ff)), norms_(std::move(norms)), width_(width) {}
     virtual ~Block() = default;
     virtual void forward(StepContext& ctx, Tensor& x, const LayerCall& call) = 0;
+    // What the layer asks of the cache manager: the mixer's needs, plus whatever the block itself keeps per request.
+    virtual CacheSpec cache_spec() const { return mixer_->cache_spec(); }
     Mixer& mixer() { return *mixer_; }
     FeedForward& feed_forward() { return *ff_; }
     std::map<std::string, std::unique_ptr<Norm>>& norms() { return norms_; }
+    std::map<std::string, std::unique_ptr<Wrap>>& wraps() { return wraps_; }
 protected:
     std::unique_ptr<Mixer> mixer_;
     std::unique_ptr<FeedForward> ff_;
     std::map<std::string, std::unique_ptr<Norm>> norms_;
+    std::map<std::string, std::unique_ptr<Wrap>> wraps_;
     int64_t width_;
 };
 
@@ -225,6 +257,7 @@ struct BlockParts {
     std::unique_ptr<Mixer> mixer;
     std::unique_ptr<FeedForward> feed_forward;
     std::map<std::string, std::unique_ptr<Norm>> norms;
+    std::map<std::string, std::unique_ptr<Wrap>> wraps;
     int64_t width = 0;
     Json params = Json::object();          // the block's own constants (LayerSpec::block_params)
 };
@@ -233,7 +266,7 @@ struct PartFactory {
     std::function<std::unique_ptr<Block>(BlockParts)> make_block;              // "block"
     std::vector<std::string> norm_names;                                       // "block": the norms it wants
 };
-// family: "mixer", "feed_forward", "norm", "position", "embedding", "head", "remix" or "block"
+// family: "mixer", "feed_forward", "norm", "position", "embedding", "head", "remix", "wrap" or "block"
 void register_part(const std::string& family, const std::string& kind, PartFactory factory);
 const PartFactory& get_part(const std::string& family, const std::string& kind);    // unknown -> ConfigError listing the known kinds
 std::vector<std::string> part_kinds(const std::string& family);
@@ -247,6 +280,11 @@ void register_capped_parts();
 // Kinds of parts_latent.cpp: attention over a latent of keys and values, a routed mixture of experts, a factor per
 // channel behind a sublayer, the block whose two sublayers read one normed input.
 void register_latent_parts();
+
+// Kinds of parts_streams.cpp: a token embedding with a hashed pair-of-tokens table, the wrap and the block of a residual
+// stream kept in several copies (with a short convolution on a sublayer's input and a gate on its result), attention
+// with a learned bias by distance, and the state-space mixer with one decay per head.
+void register_stream_parts();
 
 template <typename T>
 std::unique_ptr<T> make_part(const std::string& family, const PartSpec& spec) {

@@ -152,12 +152,19 @@ private:
 //   activation   "relu_squared": an expert is down(relu(up h)^2);
 //                "clamped_glu":  g = min(gate h, limit), u = clamp(up h, -limit, limit), down(g sigmoid(glu_alpha g) (u + 1))
 //                (parameters limit, glu_alpha)
+//                "silu_glu":     down(silu(gate h) (up h))
+//   n_identity   that many further router outputs, behind the experts with matrices, are experts that hand their input
+//                on: weight * h (gated activations only)
+//   shared_inner > 0: one more expert of that inner size ("shared.gate", "shared.up", "shared.down"), which every token
+//                passes and which is added unweighted
 //   scoring      "softmax_top": the `top` largest router logits (+ router_bias) are chosen, weighted by the softmax over
 //                the chosen logits alone (parameter router_bias);
 //                "sigmoid": scores s = sigmoid(logit); the choice is by s + correction (parameter correction: whether
 //                the tensor exists) among the experts of the keep_groups best of n_groups equal groups of neighbours (a
 //                group's score: the sum of its group_rank largest choice scores); the weights are the chosen s over their
-//                sum (+ weight_eps), times weight_scale.
+//                sum (+ weight_eps), times weight_scale;
+//                "softmax_all": scores s = softmax over ALL router outputs; the choice is by s + correction; the weights
+//                are the chosen s themselves times weight_scale (over their sum + weight_eps only with renormalize).
 // Tensors: "router" [n_experts, width], "router_bias" / "correction" [n_experts], "up.<k>" [inner, width], "gate.<k>"
 // likewise (clamped_glu), "down.<k>" [width, inner].
 // x (+)= sum over a token's chosen experts of weight * expert_k(h).  Router logits are a product written in 32-bit;
@@ -166,14 +173,22 @@ class RoutedExperts : public FeedForward {
 public:
     explicit RoutedExperts(const PartSpec& s)
         : FeedForward(s), width_(s.get_int("width")), inner_(s.get_int("inner")), E_((int)s.get_int("n_experts")),
-          top_((int)s.get_int("top")), has_bias_(s.get_bool("router_bias", false)), router_(width_, E_, false, "out_in", "router") {
-        if (E_ < 1 || E_ > 2048 || top_ < 1 || top_ > E_) throw ConfigError("routed_experts: n_experts must be 1 .. 2048 and top 1 .. n_experts");
+          top_((int)s.get_int("top")), identity_((int)s.get_int("n_identity", 0)), shared_inner_(s.get_int("shared_inner", 0)),
+          has_bias_(s.get_bool("router_bias", false)), router_(width_, E_ + identity_, false, "out_in", "router"),
+          shared_gate_up_(width_, 2 * std::max<int64_t>(shared_inner_, 1), false, "out_in", "shared_gate_up"),
+          shared_down_(std::max<int64_t>(shared_inner_, 1), width_, false, "out_in", "shared_down") {
+        if (E_ < 1 || identity_ < 0 || E_ + identity_ > 2048 || top_ < 1 || top_ > E_ + identity_)
+            throw ConfigError("routed_experts: n_experts + n_identity must be 1 .. 2048 and top 1 .. their sum");
+        if (shared_inner_ < 0) throw ConfigError("routed_experts: shared_inner must not be negative");
         const std::string a = s.get_string("activation", "relu_squared");
         if (a == "clamped_glu") {
             glu_ = true;
             limit_ = (float)s.get_double("limit");
             alpha_ = (float)s.get_double("glu_alpha", 1.0);
             if (!(limit_ > 0.0f)) throw ConfigError("routed_experts: limit must be positive");
+        } else if (a == "silu_glu") {
+            glu_ = true;
+            plain_glu_ = true;
         } else if (a != "relu_squared") {
             throw ConfigError("routed_experts: unknown activation '" + a + "'");
         }
@@ -189,14 +204,26 @@ public:
             if (rule_.n_groups < 1 || E_ % rule_.n_groups || rule_.keep_groups < 1 || rule_.keep_groups > rule_.n_groups ||
                 rule_.group_rank < 1 || top_ > E_ / rule_.n_groups * rule_.keep_groups)
                 throw ConfigError("routed_experts: n_groups must divide n_experts, 1 <= keep_groups <= n_groups, and the kept groups must hold top experts");
+        } else if (sc == "softmax_all") {
+            softmax_all_ = true;
+            has_bias_ = s.get_bool("correction", false);
+            soft_.weight_scale = (float)s.get_double("weight_scale", 1.0);
+            soft_.renormalize = s.get_bool("renormalize", false);
+            soft_.norm_eps = (float)s.get_double("weight_eps", 0.0);
         } else if (sc != "softmax_top") {
             throw ConfigError("routed_experts: unknown scoring '" + sc + "'");
         }
+        if ((identity_ > 0 || shared_inner_ > 0) && !glu_) throw ConfigError("routed_experts: identity and shared experts go with a gated activation");
     }
     TensorRequests requests() const override {
         TensorRequests t;
-        t["router"] = want({(int64_t)E_, width_});
-        if (has_bias_) t[scored_ ? "correction" : "router_bias"] = want({(int64_t)E_}, "bias");
+        t["router"] = want({(int64_t)(E_ + identity_), width_});
+        if (has_bias_) t[scored_ || softmax_all_ ? "correction" : "router_bias"] = want({(int64_t)(E_ + identity_)}, "bias");
+        if (shared_inner_) {
+            t["shared.gate"] = want({shared_inner_, width_});
+            t["shared.up"] = want({shared_inner_, width_});
+            t["shared.down"] = want({width_, shared_inner_});
+        }
         for (int e = 0; e < E_; e++) {
             t["up." + std::to_string(e)] = want({inner_, width_});
             if (glu_) t["gate." + std::to_string(e)] = want({inner_, width_});
@@ -208,7 +235,14 @@ public:
         TensorMap m;
         m["router.weight"] = t.at("router");
         router_.bind(m, dtype);
-        if (has_bias_) bias_ = to_device(t.at(scored_ ? "correction" : "router_bias"), DType::F32);
+        if (has_bias_) bias_ = to_device(t.at(scored_ || softmax_all_ ? "correction" : "router_bias"), DType::F32);
+        if (shared_inner_) {
+            TensorMap sm;
+            sm["shared_gate_up.weight"] = stack_rows({&t.at("shared.gate"), &t.at("shared.up")}, width_);
+            sm["shared_down.weight"] = t.at("shared.down");
+            shared_gate_up_.bind(sm, dtype);
+            shared_down_.bind(sm, dtype);
+        }
         std::vector<const HostTensor*> ups, downs;
         for (int e = 0; e < E_; e++) {
             if (glu_) ups.push_back(&t.at("gate." + std::to_string(e)));      // an expert's rows: its gate, then its up
@@ -219,43 +253,63 @@ public:
         down_ = to_device(stack_rows(downs, inner_), dtype);
     }
     // a decode step reads the router and, per token, `top` experts
-    size_t weight_bytes() const override { return router_.weight_bytes() + (up_.bytes() + down_.bytes()) / (size_t)E_ * (size_t)top_; }
+    size_t weight_bytes() const override {
+        return router_.weight_bytes() + (up_.bytes() + down_.bytes()) / (size_t)E_ * (size_t)std::min(top_, E_) +
+               (shared_inner_ ? shared_gate_up_.weight_bytes() + shared_down_.weight_bytes() : 0);
+    }
     bool can_overwrite() const override { return true; }
     void forward(StepContext& ctx, NormedInput& h, Tensor& x) override {
         const int64_t T = h.rows(), slots = T * top_;
         Workspace& ws = *ctx.workspace;
         const ops::Launch& l = ctx.launch;
-        Tensor logits = ws.get("moe_logits", T, E_, DType::F32);
+        const int routed = E_ + identity_;
+        Tensor logits = ws.get("moe_logits", T, routed, DType::F32);
         router_.run(ctx, &h, nullptr, logits, ops::Act::None, nullptr);
         ops::Routing r;
-        r.n_tokens = (int)T; r.n_experts = E_; r.top = top_;
+        r.n_tokens = (int)T; r.n_experts = routed; r.top = top_;
         r.expert_of = (int*)ws.raw("moe_expert_of", (size_t)slots * sizeof(int));
         r.weight_of = (float*)ws.raw("moe_weight_of", (size_t)slots * sizeof(float));
-        r.group_start = (int*)ws.raw("moe_group_start", (size_t)(E_ + 1) * sizeof(int));
+        r.group_start = (int*)ws.raw("moe_group_start", (size_t)(routed + 1) * sizeof(int));
         r.entry_of_slot = (int*)ws.raw("moe_entry_of_slot", (size_t)slots * sizeof(int));
         r.slot_of_entry = (int*)ws.raw("moe_slot_of_entry", (size_t)slots * sizeof(int));
         if (scored_) ops::moe_route_scored(l, logits, has_bias_ ? &bias_.view : nullptr, rule_, r);
+        else if (softmax_all_) ops::moe_route_softmax(l, logits, has_bias_ ? &bias_.view : nullptr, soft_, r);
         else ops::moe_route(l, logits, has_bias_ ? &bias_.view : nullptr, r);
+        // Experts without matrices come last, so the slots of those with matrices are the first group_start[E_] of the
+        // sorted order: the products walk the experts that have matrices and never see the others' slots.
+        const ops::Routing all = r;
+        r.n_experts = E_;
         Tensor a = ws.get("moe_inner", slots, inner_, ctx.compute_dtype);
         Tensor sorted = ws.get("moe_sorted_rows", slots, width_, ctx.compute_dtype);      // for steps whose products want them
         if (glu_) {
             Tensor gu = ws.get("moe_gate_up", slots, 2 * inner_, ctx.compute_dtype);
             ops::expert_product(l, r, h.tensor(), true, up_.view, ops::ExpertAct::None, gu, &sorted);
-            ops::glu_clamped(l, gu.col_range(0, inner_), gu.col_range(inner_, 2 * inner_), limit_, alpha_, a);
+            if (plain_glu_) ops::glu(l, gu.col_range(0, inner_), gu.col_range(inner_, 2 * inner_), ops::GluAct::Silu, a);
+            else ops::glu_clamped(l, gu.col_range(0, inner_), gu.col_range(inner_, 2 * inner_), limit_, alpha_, a);
         } else {
             ops::expert_product(l, r, h.tensor(), true, up_.view, ops::ExpertAct::ReluSquared, a, &sorted);
         }
         Tensor rows = ws.get("moe_rows", slots, width_, DType::F32);
         ops::expert_product(l, r, a, false, down_.view, ops::ExpertAct::None, rows);
-        ops::moe_combine(l, r, rows, x, !ctx.overwrite);
+        if (identity_) ops::moe_combine_identity(l, all, E_, h.tensor(), rows, x, !ctx.overwrite);
+        else ops::moe_combine(l, r, rows, x, !ctx.overwrite);
+        if (shared_inner_) {                        // an expert every token passes, added to the routed ones
+            Tensor sgu = ws.get("ff_gate_up", T, 2 * shared_inner_, ctx.compute_dtype);
+            shared_gate_up_.run(ctx, &h, nullptr, sgu, ops::Act::None, nullptr);
+            Tensor sa = ws.get("ff_inner", T, shared_inner_, ctx.compute_dtype);
+            ops::glu(l, sgu.col_range(0, shared_inner_), sgu.col_range(shared_inner_, 2 * shared_inner_), ops::GluAct::Silu, sa);
+            shared_down_.run(ctx, nullptr, &sa, x, ops::Act::None, &x);
+        }
     }
 private:
     int64_t width_, inner_;
-    int E_, top_;
-    bool has_bias_, glu_ = false, scored_ = false;
+    int E_, top_, identity_;
+    int64_t shared_inner_;
+    bool has_bias_, glu_ = false, plain_glu_ = false, scored_ = false, softmax_all_ = false;
     float limit_ = 0.0f, alpha_ = 1.0f;
     ops::ScoredRoute rule_;
-    Linear router_;
+    ops::SoftmaxRoute soft_;
+    Linear router_, shared_gate_up_, shared_down_;
     DeviceWeight bias_, up_, down_;
 };
 

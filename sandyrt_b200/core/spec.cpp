@@ -54,7 +54,7 @@ std::optional<int64_t> PartSpec::get_optional_int(const std::string& key) const 
 int ModelSpec::n_caches() const {
     int n = 0;
     for (const auto& c : schedule) n = std::max(n, c.cache + 1);
-    return n;
+    return std::max(n, embedding_cache + 1);
 }
 
 Json to_json(const PartSpec& p) {
@@ -85,6 +85,9 @@ Json to_json(const ModelSpec& s) {
         Json norms = Json::object();
         for (const auto& kv : l.norms) norms[kv.first] = to_json(kv.second);
         lj["norms"] = norms;
+        Json wraps = Json::object();
+        for (const auto& kv : l.wraps) wraps[kv.first] = to_json(kv.second);
+        lj["wraps"] = wraps;
         layers.push(lj);
     }
     j["layers"] = layers;
@@ -110,6 +113,8 @@ Json to_json(const ModelSpec& s) {
     for (const auto& p : s.ignored_tensors) ignored.push(p);
     j["ignored_tensors"] = ignored;
     j["eos_token_id"] = s.eos_token_id ? Json((long long)*s.eos_token_id) : Json();
+    j["streams"] = (long long)s.streams;
+    j["embedding_cache"] = (long long)s.embedding_cache;
     return j;
 }
 
@@ -146,6 +151,9 @@ ModelSpec model_spec_from_json(const Json& j) {
             l.mixer = part_spec_from_json(lj.at("mixer"));
             l.feed_forward = part_spec_from_json(lj.at("feed_forward"));
             for (const auto& m : lj.at("norms").members()) l.norms[m.first] = part_spec_from_json(m.second);
+            if (const Json* w = lj.find("wraps"))
+                if (w->is_object())
+                    for (const auto& m : w->members()) l.wraps[m.first] = part_spec_from_json(m.second);
             s.layers.push_back(std::move(l));
         }
         for (const Json& cj : j.at("schedule").items()) {
@@ -170,6 +178,10 @@ ModelSpec model_spec_from_json(const Json& j) {
             for (const Json& v : p->items()) s.ignored_tensors.push_back(v.as_string());
         if (const Json* e = j.find("eos_token_id"))
             if (!e->is_null()) s.eos_token_id = e->as_int();
+        if (const Json* e = j.find("streams"))
+            if (!e->is_null()) s.streams = (int)e->as_int();
+        if (const Json* e = j.find("embedding_cache"))
+            if (!e->is_null()) s.embedding_cache = (int)e->as_int();
     } catch (const ValueError& e) {
         throw ConfigError(std::string("model description is malformed: ") + e.what());
     }

@@ -48,6 +48,10 @@ struct LayerSpec {
     PartSpec mixer;
     PartSpec feed_forward;
     std::map<std::string, PartSpec> norms;   // the block kind names the norms it wants
+    // Parts of family "wrap": what a block puts around a sublayer (how the sublayer reads the stream and how its result
+    // joins it), by the sublayer's name ("mixer", "feed_forward").  Blocks that add a sublayer's result to one stream
+    // have none.
+    std::map<std::string, PartSpec> wraps;
 };
 
 // One entry of the run order.  `layer` indexes ModelSpec::layers (a layer may be named by several
@@ -82,6 +86,12 @@ struct ModelSpec {
     // Regular expressions for tensors that a file may hold and the model does not read.
     std::vector<std::string> ignored_tensors;
     std::optional<int64_t> eos_token_id;
+    // Copies of the residual stream: with more than one, the embedding's output enters all of them, the blocks work on
+    // [tokens, streams * width], and the final norm reads their sum.
+    int streams = 1;
+    // The cache entry (a fixed-size state) of the embedding, for embeddings that remember something of a request
+    // between steps; -1: none.
+    int embedding_cache = -1;
 
     int n_caches() const;
 };

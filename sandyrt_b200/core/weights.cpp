@@ -15,6 +15,14 @@ namespace sandy {
 
 namespace {
 
+// A requested size of -1 takes whatever the file has there (a table whose length the file decides).
+bool shape_fits(const std::vector<int64_t>& got, const std::vector<int64_t>& want) {
+    if (got.size() != want.size()) return false;
+    for (size_t i = 0; i < got.size(); i++)
+        if (want[i] != -1 && want[i] != got[i]) return false;
+    return true;
+}
+
 std::string shape_text(const std::vector<int64_t>& s) {
     std::string out = "[";
     for (size_t i = 0; i < s.size(); i++) out += (i ? ", " : "") + std::to_string(s[i]);
@@ -64,7 +72,7 @@ TensorMap load_weights(const std::string& model_dir, const TensorRequests& reque
     for (const auto& kv : requests) {
         const std::string full = prefix + kv.first;
         if (!f.contains(full)) { missing.push_back(full); continue; }
-        if (f.shape(full) != kv.second.shape) wrong_shape.push_back({full, f.shape(full), kv.second.shape});
+        if (!shape_fits(f.shape(full), kv.second.shape)) wrong_shape.push_back({full, f.shape(full), kv.second.shape});
         if (store_dtype_is_float(f.dtype(full)) == kv.second.integer)
             wrong_kind.emplace_back(full, store_dtype_word(f.dtype(full)));
     }
@@ -157,6 +165,8 @@ TensorMap random_tensors(const TensorRequests& requests, uint64_t seed, StoreDTy
         const TensorRequest& req = kv.second;
         HostTensor t;
         t.shape = req.shape;
+        for (int64_t d : t.shape)
+            if (d < 0) throw ConfigError("tensor '" + kv.first + "' takes a size from the weight file; random weights need it in the configuration");
         const int64_t n = t.numel();
         if (req.integer) {
             t.dtype = StoreDType::I32;

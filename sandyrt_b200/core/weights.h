@@ -25,7 +25,7 @@ namespace sandy {
 
 // What a part expects of one tensor of the weight file.
 struct TensorRequest {
-    std::vector<int64_t> shape;
+    std::vector<int64_t> shape;  // a size of -1 takes whatever the file has there (the part then reads it when it binds)
     bool integer = false;        // an integer table (kept as int32) rather than floats
     bool keep_32bit = false;     // if stored as F32, stay F32 whatever the compute dtype
     // How the random-weights mode fills it: "weight" N(0, 0.02), "bias" N(0, 0.01),

@@ -3,6 +3,8 @@
 // Formula, as the reference computes it (src/core/TensorCalc.cpp:1241-1311):
 //   s[j] = (q . k_j) * scale            for  max(0, pos+1-window) <= j <= pos   (window 0: all)
 //   p[j] = exp(s[j] - max s) / sum exp(s - max s);   o = sum_j p[j] * v_j
+// A learned bias by distance may join a score: row min(pos - j, n_dist - 1) of a table [n_dist, H], added after the
+// scale (and the cap).
 // Two rules some layers add: with softcap > 0 a score becomes softcap * tanh(s / softcap) before the softmax; with
 // chunk > 0 a query at position pos sees only keys of its own chunk, j >= pos - pos % chunk (chunks are counted from
 // position 0 of the request, wherever the step's tokens start).
@@ -104,7 +106,8 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
                        T* __restrict__ out, int ld_out,
                        int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
                        float scale, int window, float softcap, int chunk, int num_pages,
-                       const float* __restrict__ sink, const float* __restrict__ out_gate, int* __restrict__ status) {
+                       const float* __restrict__ sink, const float* __restrict__ out_gate,
+                       const float* __restrict__ dist_bias, int n_dist, int* __restrict__ status) {
     __shared__ float q_smem[WARPS_PER_BLOCK][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long pair = (long long)blockIdx.x * WARPS_PER_BLOCK + warp;
@@ -141,6 +144,7 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
                 row = (long long)page * rows_per_page + (long long)kvh * page_size + (j % page_size);
                 sc = dot_row<T>(k_cache + row * head_dim, qs, head_dim) * scale;
                 if (softcap > 0.0f) sc = softcap * tanhf(sc / softcap);
+                if (dist_bias) sc += dist_bias[(size_t)min(pos - j, n_dist - 1) * n_heads + h];
             }
         }
         const float m_new = fmaxf(m, warp_max(sc));
@@ -205,13 +209,17 @@ SANDY_API int sandy_kv_append(const void* k_src, const void* v_src, int ld_src,
 // window 0 = every earlier key is visible.  sink: float32 [H] or null: exp(sink[h]) joins the softmax's
 // denominator.  out_gate: float32 [n_tokens, H] or null: a factor on each head's output.
 // out_gate: float32 [n_tokens, H] or null: a factor on each head's output.  softcap 0: scores as they are; chunk 0: no chunks.
-SANDY_API int sandy_paged_attention_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache,
-                                        long long page_stride, const int* block_table, int max_blocks,
-                                        const int* token_seq, const int* positions, void* out, int ld_out,
-                                        int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                        float scale, int window, float softcap, int chunk, int num_pages, int dtype,
-                                        const float* sink, const float* out_gate, int* status, cudaStream_t stream) {
+// dist_bias: float32 [n_dist, H] or null: row min(i - j, n_dist - 1) is added to the score of query i and key j (after the
+// scale and the cap), a learned bias by distance.
+SANDY_API int sandy_paged_attention_bias(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                         long long page_stride, const int* block_table, int max_blocks,
+                                         const int* token_seq, const int* positions, void* out, int ld_out,
+                                         int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                         float scale, int window, float softcap, int chunk, int num_pages, int dtype,
+                                         const float* sink, const float* out_gate, const float* dist_bias, int n_dist,
+                                         int* status, cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
+    if (dist_bias && n_dist < 1) return SANDY_ERR_ARGUMENT;
     if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out)
         return SANDY_ERR_ARGUMENT;
     if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > WIDE_HEAD_DIM) return SANDY_ERR_UNSUPPORTED;
@@ -223,12 +231,24 @@ SANDY_API int sandy_paged_attention_cap(const void* q, int ld_q, const void* k_c
     (head_dim <= MAX_HEAD_DIM ? paged_attention_kernel<T, MAX_HEAD_DIM> : paged_attention_kernel<T, WIDE_HEAD_DIM>)<<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>( \
         (const T*)q, ld_q, (const T*)k_cache, (const T*)v_cache, page_stride, block_table, max_blocks, \
         token_seq, positions, (T*)out, ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size,    \
-        scale, window, softcap, chunk, num_pages, sink, out_gate, status)
+        scale, window, softcap, chunk, num_pages, sink, out_gate, dist_bias, n_dist, status)
     if (dtype == SANDY_F32) LAUNCH(float);
     else if (dtype == SANDY_BF16) LAUNCH(bf16);
     else return SANDY_ERR_UNSUPPORTED;
 #undef LAUNCH
     return sandy_launch_status();
+}
+
+// The same without a bias by distance.
+SANDY_API int sandy_paged_attention_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                        long long page_stride, const int* block_table, int max_blocks,
+                                        const int* token_seq, const int* positions, void* out, int ld_out,
+                                        int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                        float scale, int window, float softcap, int chunk, int num_pages, int dtype,
+                                        const float* sink, const float* out_gate, int* status, cudaStream_t stream) {
+    return sandy_paged_attention_bias(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq, positions, out,
+                                      ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size, scale, window, softcap, chunk,
+                                      num_pages, dtype, sink, out_gate, nullptr, 0, status, stream);
 }
 
 // The same with plain scores and no chunks.

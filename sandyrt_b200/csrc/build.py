@@ -56,6 +56,8 @@ LIBRARIES: Dict[str, List[str]] = {
     "grouped_gemm": [],
     "grouped_gemm_tc": [],
     "moe": [],
+    "streams": [],
+    "ssm_state": [],
 }
 
 

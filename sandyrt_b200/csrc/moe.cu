@@ -9,6 +9,9 @@
 //                      scores, and only experts of the `keep_groups` best groups can be chosen (ties: the lower group
 //                      and the lower expert first); the `top` largest c among those are chosen; their weights are
 //                      their s over the sum of the chosen s (+ norm_eps), times weight_scale.
+//   sandy_moe_route_softmax
+//                      per token: scores s = softmax(z) over all experts; the `top` largest s + correction are chosen;
+//                      their weights are their s themselves (not renormalised unless asked).
 //   sandy_moe_group    entries sorted by expert: group_start[e] .. group_start[e+1]-1 are expert e's slots;
 //                      entry_of_slot and slot_of_entry are the two directions of the permutation.  Which slot of
 //                      its expert an entry gets is not fixed from run to run; nothing depends on it, since every
@@ -16,6 +19,9 @@
 //   sandy_moe_gather   sorted[s] = x[token of slot s]: the tokens' rows in the order of the slots, for a product that
 //                      wants every expert's rows one after another.
 //   sandy_moe_combine  y[t] (+)= sum_j weight[t, j] * rows[slot_of_entry[t * top + j]], in 32-bit, j in order.
+//   sandy_moe_combine_identity
+//                      the same where the last experts are identities: their entries contribute weight * the token's
+//                      own input row.
 #include "common.cuh"
 
 namespace {
@@ -64,7 +70,8 @@ moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restri
 __global__ void __launch_bounds__(128)
 moe_route_scored_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction, int n_tokens,
                         int n_experts, int top, int n_groups, int keep_groups, int group_rank, float weight_scale,
-                        float norm_eps, int* __restrict__ expert_of, float* __restrict__ weight_of) {
+                        float norm_eps, int softmax_scores, int renormalize, int* __restrict__ expert_of,
+                        float* __restrict__ weight_of) {
     extern __shared__ float route_smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -74,8 +81,17 @@ moe_route_scored_kernel(const float* __restrict__ logits, int ld, const float* _
     float* c = route_smem + (size_t)warp * (2 * n_experts + n_groups);
     float* sc = c + n_experts;
     float* gs = sc + n_experts;
+    float z_max = -INFINITY, z_sum = 1.0f;
+    if (softmax_scores) {                            // s = softmax over all experts' logits
+        for (int e = lane; e < n_experts; e += 32) z_max = fmaxf(z_max, logits[(size_t)t * ld + e]);
+        z_max = warp_max(z_max);
+        float part = 0.0f;
+        for (int e = lane; e < n_experts; e += 32) part += expf(logits[(size_t)t * ld + e] - z_max);
+        z_sum = warp_sum(part);
+    }
     for (int e = lane; e < n_experts; e += 32) {
-        const float s = 1.0f / (1.0f + expf(-logits[(size_t)t * ld + e]));
+        const float z = logits[(size_t)t * ld + e];
+        const float s = softmax_scores ? expf(z - z_max) / z_sum : 1.0f / (1.0f + expf(-z));
         sc[e] = s;
         c[e] = s + (correction ? correction[e] : 0.0f);
     }
@@ -134,7 +150,8 @@ moe_route_scored_kernel(const float* __restrict__ logits, int ld, const float* _
         }
         __syncwarp();
     }
-    for (int j = lane; j < top; j += 32) weight_of[(size_t)t * top + j] = weight_of[(size_t)t * top + j] / (sum + norm_eps) * weight_scale;
+    const float denom = renormalize ? sum + norm_eps : 1.0f;
+    for (int j = lane; j < top; j += 32) weight_of[(size_t)t * top + j] = weight_of[(size_t)t * top + j] / denom * weight_scale;
 }
 
 __global__ void __launch_bounds__(1024)
@@ -185,15 +202,21 @@ moe_gather_kernel(const V* __restrict__ x, long long ldx, const int* __restrict_
 
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ rows, int ld_rows, const float* __restrict__ weight_of,
-                   const int* __restrict__ slot_of_entry, int top, float* __restrict__ y, int ldy, int width, int add) {
+                   const int* __restrict__ slot_of_entry, int top, float* __restrict__ y, int ldy, int width, int add,
+                   const int* __restrict__ expert_of, int n_real, const void* __restrict__ h, int ldh, int h_dtype) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float acc = 0.0f;
         for (int j = 0; j < top; j++) {
-            const int s = slot_of_entry[(size_t)t * top + j];
-            acc = fmaf(weight_of[(size_t)t * top + j], rows[(size_t)s * ld_rows + c], acc);
+            float v;
+            if (expert_of && expert_of[(size_t)t * top + j] >= n_real) {      // an expert that hands its input on
+                v = h_dtype == SANDY_BF16 ? to_f32(((const bf16*)h)[(size_t)t * ldh + c]) : ((const float*)h)[(size_t)t * ldh + c];
+            } else {
+                v = rows[(size_t)slot_of_entry[(size_t)t * top + j] * ld_rows + c];
+            }
+            acc = fmaf(weight_of[(size_t)t * top + j], v, acc);
         }
         float* dst = y + (size_t)t * ldy + c;
         *dst = add ? *dst + acc : acc;
@@ -227,7 +250,21 @@ SANDY_API int sandy_moe_route_scored(const float* logits, int ld, const float* c
     const int warps = 4;
     return sandy_launch(moe_route_scored_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps),
                         (size_t)warps * (2 * n_experts + n_groups) * sizeof(float), stream, logits, ld, correction, n_tokens,
-                        n_experts, top, n_groups, keep_groups, group_rank, weight_scale, norm_eps, expert_of, weight_of);
+                        n_experts, top, n_groups, keep_groups, group_rank, weight_scale, norm_eps, 0, 1, expert_of, weight_of);
+}
+
+// Scores s = softmax over ALL experts' logits; the choice is by s + correction (ties: the lower expert first); the
+// weights are the chosen experts' s themselves, times weight_scale, over their sum (+ norm_eps) only with renormalize.
+SANDY_API int sandy_moe_route_softmax(const float* logits, int ld, const float* correction, int n_tokens, int n_experts, int top,
+                                      float weight_scale, float norm_eps, int renormalize, int* expert_of, float* weight_of,
+                                      cudaStream_t stream) {
+    if (n_tokens == 0) return SANDY_OK;
+    if (!logits || !expert_of || !weight_of) return SANDY_ERR_ARGUMENT;
+    if (top < 1 || top > n_experts || n_experts > 2048) return SANDY_ERR_UNSUPPORTED;
+    const int warps = 4;
+    return sandy_launch(moe_route_scored_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps),
+                        (size_t)warps * (2 * n_experts + 1) * sizeof(float), stream, logits, ld, correction, n_tokens, n_experts,
+                        top, 1, 1, 1, weight_scale, norm_eps, 1, renormalize, expert_of, weight_of);
 }
 
 SANDY_API int sandy_moe_group(const int* expert_of, int n_entries, int n_experts, int* group_start, int* entry_of_slot,
@@ -244,7 +281,19 @@ SANDY_API int sandy_moe_combine(const float* rows, int ld_rows, const float* wei
     if (n_tokens == 0 || width == 0) return SANDY_OK;
     if (!rows || !weight_of || !slot_of_entry || !y) return SANDY_ERR_ARGUMENT;
     return sandy_launch(moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, rows, ld_rows, weight_of, slot_of_entry, top,
-                        y, ldy, width, add);
+                        y, ldy, width, add, (const int*)nullptr, 0, (const void*)nullptr, 0, SANDY_F32);
+}
+
+// The same where the experts from n_real on have no matrices and hand their input on: an entry whose expert_of is
+// n_real or more contributes weight * h[t] (h [n_tokens, width] of h_dtype) instead of a computed row.
+SANDY_API int sandy_moe_combine_identity(const float* rows, int ld_rows, const float* weight_of, const int* slot_of_entry,
+                                         const int* expert_of, int n_real, const void* h, int ldh, int h_dtype, int n_tokens,
+                                         int top, float* y, int ldy, int width, int add, cudaStream_t stream) {
+    if (n_tokens == 0 || width == 0) return SANDY_OK;
+    if (!rows || !weight_of || !slot_of_entry || !y || !expert_of || !h) return SANDY_ERR_ARGUMENT;
+    if (h_dtype != SANDY_F32 && h_dtype != SANDY_BF16) return SANDY_ERR_UNSUPPORTED;
+    return sandy_launch(moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, rows, ld_rows, weight_of, slot_of_entry, top,
+                        y, ldy, width, add, expert_of, n_real, h, ldh, h_dtype);
 }
 
 // x: [tokens, bytes_per_row] and out: [n_slots, bytes_per_row] as raw bytes with pitches in bytes; pieces of 16 bytes

@@ -116,6 +116,13 @@ int sandy_paged_attention_cap(const void* q, int ld_q, const void* k_cache, cons
                               int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
                               int window, float softcap, int chunk, int num_pages, int dtype, const float* sink,
                               const float* out_gate, int* status, cudaStream_t stream);
+/* ... and with a learned bias by distance: row min(i - j, n_dist - 1) of dist_bias (float32 [n_dist, H]) joins the
+   score of query i and key j after the scale and the cap.  Null: none. */
+int sandy_paged_attention_bias(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                               const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
+                               int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
+                               int window, float softcap, int chunk, int num_pages, int dtype, const float* sink,
+                               const float* out_gate, const float* dist_bias, int n_dist, int* status, cudaStream_t stream);
 int sandy_prefill_attention_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
                                 const int* block_table, int max_blocks, const int* q_start, const int* kv_before, void* out,
                                 int ld_out, int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int head_dim,
@@ -187,6 +194,17 @@ int sandy_attention_prepare_ext(const void* proj, int ld, int q_off, int k_off, 
                                 int ld_gate, float* gate_out, float gate_scale, const float* q_head_scale, float v_unit_eps,
                                 int dtype, int* status, cudaStream_t stream);
 
+/* ... with every query and key head over its own root mean square (per_head_norm) and a factor on the query that grows
+   with the position, 1 + q_pos_coef * ln(floor((p + 1) / q_pos_every) + 1) (q_pos_every 0: none). */
+int sandy_attention_prepare_pos(const void* proj, int ld, int q_off, int k_off, int v_off, int n_tokens, int n_heads,
+                                int n_kv_heads, int qk_dim, int v_dim, int pad_dim, const float* q_gain, const float* k_gain,
+                                float eps, const float* freq, int rot_dims, const int* positions, const int* token_seq,
+                                const int* block_table, int max_blocks, void* k_cache, void* v_cache, long long page_stride,
+                                int page_size, int num_pages, int write_cache, void* q_out, int ld_q, const float* gate_in,
+                                int ld_gate, float* gate_out, float gate_scale, const float* q_head_scale, float v_unit_eps,
+                                int per_head_norm, float q_pos_coef, int q_pos_every, int dtype, int* status,
+                                cudaStream_t stream);
+
 /* rmsnorm.cu */
 int sandy_rmsnorm_shift(const float* x, int ldx, const float* gain, const float* mix, float* state, long long state_stride,
                         const int* token_seq, const int* q_start, const int* seq_slots, void* out, int ldo, int n_tokens,
@@ -243,6 +261,42 @@ int sandy_moe_gather(const void* x, long long pitch_x, const int* entry_of_slot,
                      int bytes_per_row, cudaStream_t stream);
 int sandy_moe_combine(const float* rows, int ld_rows, const float* weight_of, const int* slot_of_entry, int n_tokens, int top,
                       float* y, int ldy, int width, int add, cudaStream_t stream);
+
+int sandy_moe_route_softmax(const float* logits, int ld, const float* correction, int n_tokens, int n_experts, int top,
+                            float weight_scale, float norm_eps, int renormalize, int* expert_of, float* weight_of,
+                            cudaStream_t stream);
+int sandy_moe_combine_identity(const float* rows, int ld_rows, const float* weight_of, const int* slot_of_entry,
+                               const int* expert_of, int n_real, const void* h, int ldh, int h_dtype, int n_tokens, int top,
+                               float* y, int ldy, int width, int add, cudaStream_t stream);
+
+/* streams.cu */
+int sandy_streams_step(float* X, int ldX, int n_tokens, int n_streams, int width, const float* y, int ldy, const float* gate,
+                       int ldg, const float* gate_bias, const float* mix, const float* out_w, const float* in_w,
+                       const float* gain, float eps, void* h, int ldh, int h_dtype, float* sum_out, int ld_sum,
+                       cudaStream_t stream);
+int sandy_streams_max(void);
+int sandy_streams_spread(const float* x, int ldx, float* X, int ldX, int n_tokens, int n_streams, int width, cudaStream_t stream);
+int sandy_canon_conv(const void* h, int ldh, const float* taps, int n_taps, const float* state, long long state_stride,
+                     long long tail_off, const int* token_seq, const int* q_start, const int* seq_slots, void* c, int ldc,
+                     int n_tokens, int width, int dtype, cudaStream_t stream);
+int sandy_embed_bigram(const int* ids, const int* positions, const int* token_seq, const int* q_start, const int* seq_slots,
+                       const void* wte, const void* bigram, const void* wpe, int buckets, long long mul_prev, long long mul_cur,
+                       int* state, long long state_stride, float* x, int ldx, int n_tokens, int vocab, int n_pos, int width,
+                       int table_dtype, int keep, int* status, cudaStream_t stream);
+int sandy_bigram_keep(const int* ids, const int* q_start, const int* seq_slots, int* state, long long state_stride, int n_seqs,
+                      cudaStream_t stream);
+
+/* ssm_state.cu */
+long long sandy_ssm_state_floats(int n_heads, int state, int v_dim);
+int sandy_ssm_prepare(const void* proj, int ld, int dtype, int channels, const float* taps, int n_taps, const float* conv_bias,
+                      const float* dt_raw, int ld_dt, const float* dt_bias, const float* a_log, int n_heads, const float* state,
+                      long long state_stride, long long tail_off, const int* token_seq, const int* q_start, const int* seq_slots,
+                      float* xbc, int ld_xbc, float* dta, int n_tokens, cudaStream_t stream);
+int sandy_ssm_scan(const float* xbc, int ld, const float* dta, const float* d_skip, float* state, long long state_stride,
+                   const int* q_start, const int* seq_slots, float* out, int ld_out, int n_seqs, int n_heads, int n_groups,
+                   int state_dim, int v_dim, cudaStream_t stream);
+int sandy_gated_group_norm(const float* y, int ldy, const void* z, int ldz, const float* gain, float eps, int groups, void* out,
+                           int ld_out, int n_tokens, int cols, int dtype, cudaStream_t stream);
 
 /* matrix_state.cu */
 long long sandy_mlstm_state_floats(int n_heads, int qk_dim, int v_dim);

@@ -1,0 +1,242 @@
+// A selective state-space mixer with one decay per head (the recurrence of Mamba-2):
+//
+//   S_t = exp(-exp(A_log) dt_t) S_{t-1} + dt_t B_t x_t^T          S: [N, P] per head, float32, carried from step to step
+//   y_t = S_t^T C_t + D x_t                                        heads share B and C in groups
+//
+//   sandy_ssm_prepare      per token: the short causal convolution (with bias) and silu of the x, B and C channels, rows
+//                          before the step's first token of a request from the tail in its state; dt = softplus(raw +
+//                          dt_bias) and the decay's logarithm -exp(A_log) dt.  All float32.
+//   sandy_ssm_scan         the recurrence, token by token, each request from its own state.  A block owns 32 columns of
+//                          one head's state for one request; a thread owns one column and every fourth group of four
+//                          rows, so the state update needs no exchange at all and the read-out y one sum over four
+//                          neighbouring lanes.  The tokens' inputs are staged through shared memory eight at a time,
+//                          the next eight in flight meanwhile.  A step may bring any mix of portions and single tokens.
+//   sandy_gated_group_norm out = (y * silu(z)) / rms * gain over `groups` equal parts of a row, the gate BEFORE the norm
+//
+// The state of a slot is S [H][P][N] (a column's rows are consecutive floats).  Everything is float32 arithmetic whatever
+// the engine's compute type; inputs that come from a projection are read in the projection's type.  The recurrence
+// stays on the FMA pipe on purpose: the state and everything that enters it are 32-bit by the designs that use it, and
+// in this token-by-token form it costs 3 N P operations a token and head, fewer than the chunked forms that trade
+// operations for tensor-core shapes.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_TAPS = 8;
+constexpr int COLS = 32;                       // columns of a head's state per block
+constexpr int THREADS = 128;                   // 32 columns x 4 row slices
+constexpr int CHUNK = 8;                       // tokens staged at a time
+
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+ssm_prepare_kernel(const T* __restrict__ proj, int ld, int channels, const float* __restrict__ taps, int n_taps,
+                   const float* __restrict__ conv_bias, const float* __restrict__ dt_raw, int ld_dt,
+                   const float* __restrict__ dt_bias, const float* __restrict__ a_log, int n_heads,
+                   const float* __restrict__ state, long long state_stride, long long tail_off,
+                   const int* __restrict__ token_seq, const int* __restrict__ q_start, const int* __restrict__ seq_slots,
+                   float* __restrict__ xbc, int ld_xbc, float* __restrict__ dta) {
+    const int t = blockIdx.x;
+    const int s = token_seq[t];
+    const int i_in_step = t - q_start[s];
+    const float* tail = state + (long long)seq_slots[s] * state_stride + tail_off;      // [n_taps - 1][channels]
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        float y = conv_bias ? conv_bias[c] : 0.0f;
+        for (int j = 0; j < n_taps; j++) {
+            const int lag = n_taps - 1 - j;
+            const int src = i_in_step - lag;
+            const float x = src >= 0 ? to_f32(proj[(size_t)(t - lag) * ld + c]) : tail[(size_t)(n_taps - 1 + src) * channels + c];
+            y = fmaf(taps[(size_t)c * n_taps + j], x, y);
+        }
+        xbc[(size_t)t * ld_xbc + c] = silu_f(y);
+    }
+    for (int h = threadIdx.x; h < n_heads; h += blockDim.x) {
+        const float dt = softplus_f(dt_raw[(size_t)t * ld_dt + h] + dt_bias[h]);
+        dta[(size_t)t * 2 * n_heads + h] = dt;
+        dta[(size_t)t * 2 * n_heads + n_heads + h] = -expf(a_log[h]) * dt;
+    }
+}
+
+// xbc: float32 [T, ld] rows of (x [H * P], B [G * N], C [G * N]); dta: float32 [T, 2H] (dt, then the decay's logarithm).
+// Q: groups of four rows a thread owns; rows beyond N are zeros.  What a token brings to a block, as it lies in shared
+// memory: B [16 Q], C [16 Q], x [COLS], dt, decay.
+template <int Q>
+__global__ void __launch_bounds__(THREADS)
+ssm_scan_kernel(const float* __restrict__ xbc, int ld, const float* __restrict__ dta, const float* __restrict__ d_skip,
+                float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
+                const int* __restrict__ seq_slots, float* __restrict__ out, int ld_out, int n_heads, int n_groups, int N, int P) {
+    constexpr int NP = 16 * Q;
+    constexpr int PER = 2 * NP + COLS + 4;          // dt, the decay's logarithm, and two floats that keep a token's rows 16-byte aligned
+    __shared__ __align__(16) float stage[CHUNK * PER];
+    const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
+    const int slice = threadIdx.x & 3, col = col0 + (threadIdx.x >> 2);
+    const int g = h / (n_heads / n_groups);
+    const int t0 = q_start[s], t1 = q_start[s + 1];
+    const int inner = n_heads * P;
+    const float skip = d_skip ? d_skip[h] : 0.0f;
+    float* S = state + (long long)seq_slots[s] * state_stride + ((long long)h * P + col) * N;
+    pdl_wait();
+    float st[Q][4];
+#pragma unroll
+    for (int q = 0; q < Q; q++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int n = 16 * q + 4 * slice + e;
+            st[q][e] = (col < P && n < N) ? S[n] : 0.0f;
+        }
+    constexpr int NL = (CHUNK * PER + THREADS - 1) / THREADS;
+    float pre[NL];
+    auto fetch = [&](int tc) {
+        const int n_tok = min(CHUNK, t1 - tc);
+#pragma unroll
+        for (int x = 0; x < NL; x++) {
+            const int f = threadIdx.x + x * THREADS;
+            const int tok = f / PER, j = f % PER;
+            float v = 0.0f;
+            if (tok < n_tok) {
+                const float* row = xbc + (size_t)(tc + tok) * ld;
+                if (j < NP) v = j < N ? row[inner + g * N + j] : 0.0f;
+                else if (j < 2 * NP) v = j - NP < N ? row[inner + n_groups * N + g * N + (j - NP)] : 0.0f;
+                else if (j < 2 * NP + COLS) v = col0 + j - 2 * NP < P ? row[h * P + col0 + j - 2 * NP] : 0.0f;
+                else if (j < 2 * NP + COLS + 2) v = dta[(size_t)(tc + tok) * 2 * n_heads + (j - 2 * NP - COLS) * n_heads + h];
+            }
+            pre[x] = v;
+        }
+    };
+    if (t0 < t1) fetch(t0);
+    for (int tc = t0; tc < t1; tc += CHUNK) {
+        __syncthreads();
+#pragma unroll
+        for (int x = 0; x < NL; x++) {
+            const int f = threadIdx.x + x * THREADS;
+            if (f < CHUNK * PER) stage[f] = pre[x];
+        }
+        __syncthreads();
+        if (tc + CHUNK < t1) fetch(tc + CHUNK);
+        const int n_tok = min(CHUNK, t1 - tc);
+        for (int tok = 0; tok < n_tok; tok++) {
+            const float* in = stage + tok * PER;
+            const float xv = in[2 * NP + (threadIdx.x >> 2)];
+            const float dt = in[2 * NP + COLS], decay = expf(in[2 * NP + COLS + 1]);
+            const float dtx = dt * xv;
+            float y = 0.0f;
+#pragma unroll
+            for (int q = 0; q < Q; q++) {
+                const float4 b = *reinterpret_cast<const float4*>(in + 16 * q + 4 * slice);
+                const float4 c = *reinterpret_cast<const float4*>(in + NP + 16 * q + 4 * slice);
+                st[q][0] = fmaf(b.x, dtx, decay * st[q][0]);
+                st[q][1] = fmaf(b.y, dtx, decay * st[q][1]);
+                st[q][2] = fmaf(b.z, dtx, decay * st[q][2]);
+                st[q][3] = fmaf(b.w, dtx, decay * st[q][3]);
+                y = fmaf(st[q][0], c.x, y);
+                y = fmaf(st[q][1], c.y, y);
+                y = fmaf(st[q][2], c.z, y);
+                y = fmaf(st[q][3], c.w, y);
+            }
+            y += __shfl_xor_sync(0xffffffffu, y, 1);
+            y += __shfl_xor_sync(0xffffffffu, y, 2);
+            if (slice == 0 && col < P) out[(size_t)(tc + tok) * ld_out + h * P + col] = fmaf(skip, xv, y);
+        }
+    }
+    pdl_launch_dependents();
+    if (t0 < t1 && col < P) {
+#pragma unroll
+        for (int q = 0; q < Q; q++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int n = 16 * q + 4 * slice + e;
+                if (n < N) S[n] = st[q][e];
+            }
+    }
+}
+
+// One block per (token, part of the row).
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_group_norm_kernel(const float* __restrict__ y, int ldy, const T* __restrict__ z, int ldz, const float* __restrict__ gain,
+                        float eps, int part, T* __restrict__ out, int ld_out) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, c0 = blockIdx.y * part;
+    pdl_wait();
+    pdl_launch_dependents();
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+        const float v = y[(size_t)t * ldy + c0 + i] * silu_f(to_f32(z[(size_t)t * ldz + c0 + i]));
+        ss = fmaf(v, v, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)part + eps);
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+        const float v = y[(size_t)t * ldy + c0 + i] * silu_f(to_f32(z[(size_t)t * ldz + c0 + i]));
+        out[(size_t)t * ld_out + c0 + i] = from_f32<T>(v * inv * (gain ? gain[c0 + i] : 1.0f));
+    }
+}
+
+}  // namespace
+
+SANDY_API long long sandy_ssm_state_floats(int n_heads, int state, int v_dim) { return (long long)n_heads * state * v_dim; }
+
+// proj: [n_tokens, >= channels] of dtype with pitch ld, the x, B and C channels first (the caller passes the address of
+// their first column).  taps float32 [channels, n_taps], conv_bias float32 [channels] or null.  dt_raw float32
+// [n_tokens, >= n_heads] with pitch ld_dt.  The tail of a slot is float32 [n_taps - 1][channels] at tail_off of its state.
+// xbc float32 [n_tokens, channels] with pitch ld_xbc; dta float32 [n_tokens, 2 * n_heads].
+SANDY_API int sandy_ssm_prepare(const void* proj, int ld, int dtype, int channels, const float* taps, int n_taps,
+                                const float* conv_bias, const float* dt_raw, int ld_dt, const float* dt_bias, const float* a_log,
+                                int n_heads, const float* state, long long state_stride, long long tail_off,
+                                const int* token_seq, const int* q_start, const int* seq_slots, float* xbc, int ld_xbc,
+                                float* dta, int n_tokens, cudaStream_t stream) {
+    if (n_tokens == 0) return SANDY_OK;
+    if (!proj || !taps || !dt_raw || !dt_bias || !a_log || !token_seq || !q_start || !seq_slots || !xbc || !dta ||
+        (n_taps > 1 && !state))
+        return SANDY_ERR_ARGUMENT;
+    if (n_taps < 1 || n_taps > MAX_TAPS || channels < 1 || n_heads < 1) return SANDY_ERR_UNSUPPORTED;
+    if (dtype == SANDY_F32)
+        return sandy_launch(ssm_prepare_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)proj, ld, channels, taps,
+                            n_taps, conv_bias, dt_raw, ld_dt, dt_bias, a_log, n_heads, state, state_stride, tail_off, token_seq,
+                            q_start, seq_slots, xbc, ld_xbc, dta);
+    if (dtype == SANDY_BF16)
+        return sandy_launch(ssm_prepare_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, (const bf16*)proj, ld, channels, taps,
+                            n_taps, conv_bias, dt_raw, ld_dt, dt_bias, a_log, n_heads, state, state_stride, tail_off, token_seq,
+                            q_start, seq_slots, xbc, ld_xbc, dta);
+    return SANDY_ERR_UNSUPPORTED;
+}
+
+// d_skip float32 [n_heads] or null; out float32 [n_tokens, n_heads * v_dim].  state (N) up to 256.
+SANDY_API int sandy_ssm_scan(const float* xbc, int ld, const float* dta, const float* d_skip, float* state, long long state_stride,
+                             const int* q_start, const int* seq_slots, float* out, int ld_out, int n_seqs, int n_heads,
+                             int n_groups, int state_dim, int v_dim, cudaStream_t stream) {
+    if (n_seqs == 0) return SANDY_OK;
+    if (!xbc || !dta || !state || !q_start || !seq_slots || !out) return SANDY_ERR_ARGUMENT;
+    if (n_heads < 1 || n_groups < 1 || n_heads % n_groups || state_dim < 1 || state_dim > 256 || v_dim < 1)
+        return SANDY_ERR_UNSUPPORTED;
+    const dim3 grid(n_seqs, n_heads, (v_dim + COLS - 1) / COLS);
+    if (grid.y > 65535 || grid.z > 65535) return SANDY_ERR_UNSUPPORTED;
+#define SCAN(Q)                                                                                                              \
+    return sandy_launch(ssm_scan_kernel<Q>, grid, dim3(THREADS), 0, stream, xbc, ld, dta, d_skip, state, state_stride, q_start, \
+                        seq_slots, out, ld_out, n_heads, n_groups, state_dim, v_dim)
+    if (state_dim <= 16) SCAN(1);
+    if (state_dim <= 32) SCAN(2);
+    if (state_dim <= 64) SCAN(4);
+    if (state_dim <= 128) SCAN(8);
+    SCAN(16);
+#undef SCAN
+}
+
+// y float32 [n_tokens, cols]; z and out [n_tokens, cols] of dtype; gain float32 [cols] or null; cols = groups * part.
+SANDY_API int sandy_gated_group_norm(const float* y, int ldy, const void* z, int ldz, const float* gain, float eps, int groups,
+                                     void* out, int ld_out, int n_tokens, int cols, int dtype, cudaStream_t stream) {
+    if (n_tokens == 0 || cols == 0) return SANDY_OK;
+    if (!y || !z || !out) return SANDY_ERR_ARGUMENT;
+    if (groups < 1 || cols % groups || groups > 65535) return SANDY_ERR_UNSUPPORTED;
+    const int part = cols / groups;
+    if (dtype == SANDY_F32)
+        return sandy_launch(gated_group_norm_kernel<float>, dim3(n_tokens, groups), dim3(256), 0, stream, y, ldy, (const float*)z, ldz,
+                            gain, eps, part, (float*)out, ld_out);
+    if (dtype == SANDY_BF16)
+        return sandy_launch(gated_group_norm_kernel<bf16>, dim3(n_tokens, groups), dim3(256), 0, stream, y, ldy, (const bf16*)z, ldz,
+                            gain, eps, part, (bf16*)out, ld_out);
+    return SANDY_ERR_UNSUPPORTED;
+}

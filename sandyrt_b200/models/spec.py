@@ -46,6 +46,8 @@ class LayerSpec:
     feed_forward: PartSpec
     norms: Dict[str, PartSpec]       # the block kind names the norms it wants
     block_params: Dict[str, Any] = dataclasses.field(default_factory=dict)     # the block's own constants
+    # parts of family "wrap" by sublayer name: how a sublayer reads the stream and how its result joins it
+    wraps: Dict[str, PartSpec] = dataclasses.field(default_factory=dict)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -84,9 +86,11 @@ class ModelSpec:
     eos_token_id: Optional[int] = None
     # parts of family "remix": x <- f(x, embedding output), run where the run order names them
     remixes: Sequence[PartSpec] = ()
+    streams: int = 1                 # copies of the residual stream (the final norm reads their sum)
+    embedding_cache: int = -1        # the cache entry that holds the embedding's state per request, or -1
 
     def n_caches(self) -> int:
-        return 1 + max((c.cache for c in self.schedule), default=-1)
+        return max(1 + max((c.cache for c in self.schedule), default=-1), self.embedding_cache + 1)
 
     def to_json(self) -> Dict[str, Any]:
         return {
@@ -95,13 +99,14 @@ class ModelSpec:
             "position": self.position.to_json(),
             "layers": [{"block": l.block, "mixer": l.mixer.to_json(), "feed_forward": l.feed_forward.to_json(),
                         "norms": {k: v.to_json() for k, v in l.norms.items()},
-                        "block_params": dict(l.block_params)} for l in self.layers],
+                        "block_params": dict(l.block_params),
+                        "wraps": {k: v.to_json() for k, v in l.wraps.items()}} for l in self.layers],
             "schedule": [dict({"layer": c.layer, "cache": c.cache, "write_cache": c.write_cache},
                               **({} if c.remix is None else {"remix": c.remix})) for c in self.schedule],
             "remixes": [r.to_json() for r in self.remixes],
             "final_norm": self.final_norm.to_json(), "head": self.head.to_json(),
             "name_prefixes": list(self.name_prefixes), "ignored_tensors": list(self.ignored_tensors),
-            "eos_token_id": self.eos_token_id,
+            "eos_token_id": self.eos_token_id, "streams": self.streams, "embedding_cache": self.embedding_cache,
         }
 
     @classmethod
@@ -112,9 +117,11 @@ class ModelSpec:
             position=PartSpec.from_json(j["position"]),
             layers=[LayerSpec(l["block"], PartSpec.from_json(l["mixer"]), PartSpec.from_json(l["feed_forward"]),
                               {k: PartSpec.from_json(v) for k, v in l["norms"].items()},
-                              dict(l.get("block_params") or {})) for l in j["layers"]],
+                              dict(l.get("block_params") or {}),
+                              {k: PartSpec.from_json(v) for k, v in (l.get("wraps") or {}).items()}) for l in j["layers"]],
             schedule=[LayerCall(c["layer"], c["cache"], c.get("write_cache", True), c.get("remix")) for c in j["schedule"]],
             remixes=tuple(PartSpec.from_json(r) for r in j.get("remixes") or ()),
             final_norm=PartSpec.from_json(j["final_norm"]), head=PartSpec.from_json(j["head"]),
             name_prefixes=tuple(j.get("name_prefixes") or ("",)), ignored_tensors=tuple(j.get("ignored_tensors") or ()),
-            eos_token_id=j.get("eos_token_id"))
+            eos_token_id=j.get("eos_token_id"), streams=j.get("streams") or 1,
+            embedding_cache=-1 if j.get("embedding_cache") is None else j["embedding_cache"])

@@ -42,9 +42,11 @@ def _builtin_config_classes() -> Dict[str, Type[ModelConfig]]:
     from .config.panupel import PanupelConfig
     from .config.sovezen import SovezenConfig
     from .config.bilurax import BiluraxConfig
+    from .config.tifepel import TifepelConfig
 
     return {GPT2Config.architecture: GPT2Config, PanupelConfig.architecture: PanupelConfig,
-            SovezenConfig.architecture: SovezenConfig, BiluraxConfig.architecture: BiluraxConfig}
+            SovezenConfig.architecture: SovezenConfig, BiluraxConfig.architecture: BiluraxConfig,
+            TifepelConfig.architecture: TifepelConfig}
 
 
 def _text(s: str) -> int:
