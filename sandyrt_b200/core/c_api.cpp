@@ -581,6 +581,27 @@ Json call_model(Model& model, const std::string& m, const Json& a) {
     if (m == "tensor_requests") return requests_json(model.tensor_requests());
     if (m == "spec") return to_json(model.spec());
     if (m == "config") return model.config() ? model.config()->to_json() : Json();
+    if (m == "cache_specs") {                         // what every cache entry of the run order asks of the cache manager
+        Json out = Json::array();
+        for (const CacheSpec& c : model.cache_specs()) {
+            Json e = Json::object();
+            e["kind"] = c.kind == CacheSpec::Kind::None ? "none" : c.kind == CacheSpec::Kind::PagedKV ? "paged" : c.kind == CacheSpec::Kind::State ? "state" : "paged_state";
+            if (c.has_pages()) {
+                e["n_kv_heads"] = c.n_kv_heads;
+                e["head_dim"] = c.head_dim;
+                e["window"] = c.window;
+                e["planes"] = c.planes;
+            }
+            if (c.has_state()) {
+                Json shape = Json::array();
+                for (int64_t d : c.state_shape) shape.push((long long)d);
+                e["shape"] = shape;
+                e["dtype"] = dtype_name(c.state_dtype);
+            }
+            out.push(e);
+        }
+        return out;
+    }
     if (m == "info") {
         Json o = Json::object();
         o["graph_safe"] = model.graph_safe();

@@ -1019,7 +1019,7 @@ void streams_spread(const Launch& l, const Tensor& x, Tensor& X, int n_streams) 
 void canon_conv(const Launch& l, const StepSeqs& s, const Tensor& h, const Tensor& taps, int n_taps, const StateView& state,
                 int64_t tail_off, Tensor& c) {
     if (h.dtype != c.dtype || h.rows != c.rows || h.cols != c.cols || h.rows != s.n_tokens || taps.dtype != DType::F32 ||
-        taps.numel() != h.cols * n_taps || state.dtype != DType::F32 || tail_off + (int64_t)(n_taps - 1) * h.cols > state.row_elems)
+        taps.numel() != h.cols * n_taps || (n_taps > 1 && (state.dtype != DType::F32 || tail_off + (int64_t)(n_taps - 1) * h.cols > state.row_elems)))
         throw KernelError("canon_conv: h and c [T, width] of one type, float32 taps [width, n_taps] and a float32 state expected");
     static auto fn = SANDY_KERNEL(streams, sandy_canon_conv);
     OpTimer timer(l, "input conv", tensor_bytes(&h) + tensor_bytes(&c), 0);

@@ -36,6 +36,11 @@ class Model:
         """Name in the weight file -> expected shape, for every tensor the model reads."""
         return requests_from_json(self._h.call("tensor_requests"))
 
+    def cache_specs(self):
+        """What every cache entry of the run order asks of the cache manager: dictionaries with `kind` ("none", "paged",
+        "state", "paged_state"), the pages' `n_kv_heads`, `head_dim`, `window`, `planes` and the state's `shape`, `dtype`."""
+        return self._h.call("cache_specs")
+
     def _info(self):
         return self._h.call(self._info_method)
 
