@@ -6,6 +6,8 @@
     python bench.py --attribute [--batch B]       what each family of launches costs inside a step (leave-one-out)
     python bench.py --hybrid [--batch B]          Panupel beside GPT-2 at equal layer sizes: throughput, time per kernel class
     python bench.py --latent [--batch B]          Sovezen beside GPT-2 at equal layer sizes, likewise
+    python bench.py --capped [--chunk N]          Bilurax beside Sovezen, likewise
+    python bench.py --streams [--batch B]         Tifepel beside Panupel, likewise
     python bench.py --micro gemm|decode-attention|prefill-attention [...]   kernel micro-benchmarks
 
 Default workload: GPT-2 small (12 layers, width 768, 12 heads of 64, inner 3072, vocabulary 50257,
@@ -473,9 +475,26 @@ def capped_config(width, heads, kv_heads, ff, vocab=50257, layers=4, chunk=1024)
             "embedding": {"scale": 1.0}, "layers": [{**att, "mlp": dense if i % 2 == 0 else moe} for i in range(layers)]}
 
 
+# ---- several copies of the stream around attention and state-space layers (Tifepel) beside Panupel at equal size ------
+# State-space and attention layers in turn.  The state-space mixer has width / 64 heads of 64 with a state of 128 (its
+# input projection is then as large as the other design's q, k, v and gate together); the attention has heads of 64 on
+# a third as many key/value heads and a bias table of 32 rows that reaches 512 positions back.  Every layer routes its
+# tokens to 4 of 16 + 4 experts of ff / 8 beside a shared expert of ff / 2, which moves the weights of the other design's
+# dense feed-forward a token.  Four copies of the stream, four taps on every sublayer's input.
+def streams_config(width, heads, kv_heads, ff, vocab=50257, layers=4):
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "bias_max": 512,
+                                          "bias_rows": 32, "q_temp": {"coef": 0.5, "every": 128}}}
+    ssm = {"type": "mamba2", "mixer": {"heads": width // 64, "groups": 1, "state": 128, "vdim": 64, "conv": 4, "norm_groups": 1}}
+    moe = {"kind": "moe", "expert": {"ff": ff // 8}, "router": {"experts": 16, "identity": 4, "top": 4}, "shared": {"ff": ff // 2}}
+    return {"architecture": "Tifepel", "vocab": vocab, "width": width, "max_positions": 2048, "streams": 4, "norm": {"eps": 1e-5},
+            "canon": {"taps": 4}, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}},
+            "layers": [{**(ssm if i % 2 == 0 else att), "mlp": moe} for i in range(layers)]}
+
+
 def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int, design: str = "panupel", chunk: int = 1024) -> int:
-    """Prefill and decode throughput of a design (Panupel, Sovezen or Bilurax) at sizes that resemble real layers,
-    beside its closest relative with the same width, heads, layer count and vocabulary (GPT-2; for Bilurax, Sovezen),
+    """Prefill and decode throughput of a design (Panupel, Sovezen, Bilurax or Tifepel) at sizes that resemble real layers,
+    beside its closest relative with the same width, heads, layer count and vocabulary (GPT-2; for Bilurax, Sovezen; for
+    Tifepel, Panupel),
     both with random weights; then the device time per kernel class of both, so that like kernels can be held against
     each other.  One JSON line per size, then the tables."""
     import numpy as np
@@ -489,11 +508,13 @@ def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int, de
     layers = layers or 4
     rng = np.random.default_rng(0)
     hybrid_config = {"panupel": globals()["hybrid_config"], "sovezen": latent_config,
-                     "bilurax": lambda **kw: capped_config(chunk=chunk, **kw)}[design]
+                     "bilurax": lambda **kw: capped_config(chunk=chunk, **kw), "tifepel": streams_config}[design]
 
     def arms(sz):
         if design == "bilurax":
             return ((design, hybrid_config(layers=layers, **sz)), ("sovezen", latent_config(layers=layers, **sz)))
+        if design == "tifepel":
+            return ((design, hybrid_config(layers=layers, **sz)), ("panupel", globals()["hybrid_config"](layers=layers, **sz)))
         gpt2_raw = {**load_model_config("small"), "n_embd": sz["width"], "n_head": sz["heads"], "n_inner": None, "n_layer": layers}
         return ((design, hybrid_config(layers=layers, **sz)), ("gpt2", gpt2_raw))
 
@@ -551,6 +572,9 @@ def main() -> int:
     ap.add_argument("--capped", action="store_true",
                     help="Bilurax (capped attention in chunks behind a token shift, grouped routing) beside Sovezen at equal sizes")
     ap.add_argument("--chunk", type=int, default=1024, help="chunk of positions of --capped")
+    ap.add_argument("--streams", action="store_true",
+                    help="Tifepel (several copies of the stream around attention with a bias by distance and state-space layers, "
+                         "routed experts) beside Panupel at equal sizes")
     ap.add_argument("--micro", nargs=argparse.REMAINDER, help="run a kernel micro-benchmark (see sandyrt_b200/csrc/microbench.py)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -561,9 +585,10 @@ def main() -> int:
     if args.micro is not None:
         from sandyrt_b200.csrc import microbench
         return microbench.main(args.micro)
-    if args.hybrid or args.latent or args.capped:
+    if args.hybrid or args.latent or args.capped or args.streams:
         return hybrid(args.dtype, args.layers, args.batch, min(args.steps, 128), args.warmup,
-                      design="bilurax" if args.capped else "sovezen" if args.latent else "panupel", chunk=args.chunk)
+                      design="tifepel" if args.streams else "bilurax" if args.capped else "sovezen" if args.latent else "panupel",
+                      chunk=args.chunk)
     if args.workload:
         return workload(args.workload, args.dtype, args.layers)
     if args.profile_kernels:

@@ -500,9 +500,9 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     const double attn_bytes = 2.0 * s.kv_tokens * hkv * d * q.elem_size() + 2 * tensor_bytes(&q);
     const double attn_flops = 4.0 * s.pairs * n_heads * d;
     const std::string shape = "(H=" + std::to_string(n_heads) + ",Hkv=" + std::to_string(hkv) + ",D=" + std::to_string(d) + ")";
-    if (!db && s.max_q_len > 1 && q.dtype == DType::BF16 && d <= 128) {
+    if (s.max_q_len > 1 && q.dtype == DType::BF16 && d <= 128) {
         static const bool use_tc = env_int("SANDYRT_PREFILL_TC", 1) != 0;     // 0 keeps every head size on the mma.sync kernel
-        if (use_tc && d == 64) {
+        if (use_tc && d == 64 && !db) {                       // (the tcgen05 kernel has no form for a bias by distance)
             static auto fn = SANDY_KERNEL(attention_prefill_tc, sandy_prefill_attention_tc_cap);
             OpTimer timer(l, "attention, prompt (tcgen05)", attn_bytes, attn_flops);
             const int code = fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.q_start, s.kv_before,
@@ -510,11 +510,11 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
                                 cap, chunk, c.num_pages, sk, og, l.kernel_status, l.stream);
             if (code != -1) { check(code, "prefill_attention_tc" + shape); return; }
         }
-        static auto fn = SANDY_KERNEL(attention_prefill, sandy_prefill_attention_cap);
+        static auto fn = SANDY_KERNEL(attention_prefill, sandy_prefill_attention_bias);
         OpTimer timer(l, "attention, prompt (mma.sync)", attn_bytes, attn_flops);
         check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.q_start, s.kv_before, out.data,
                  (int)out.ld, s.n_seqs, s.max_q_len, n_heads, hkv, d, c.page_size, scale, window, cap, chunk, c.num_pages, sk, og,
-                 l.kernel_status, l.stream),
+                 db, n_dist, l.kernel_status, l.stream),
               "prefill_attention" + shape);
         return;
     }
@@ -525,21 +525,21 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     // It is two launches with a floor of 9 us, so it takes the steps with enough (token, head, key) triples.  Alone, 12
     // heads of 128 on one key/value head, us, this kernel / the best of the kernels below: 1 token x 392 keys 9.1 / 5.2;
     // 8 x 392: 9.4 / 8.7; 8 tokens x 24 heads x 392: 11.3 / 16.6; 8 x 12 x 2,000: 13.2 / 36.2.
-    // Steps with capped scores or chunks of positions: this kernel is the decode kernel that has a form for them, so it
-    // takes them all (with few keys it is one launch of one split); a chunk bounds the keys a query walks.
-    if (!db && s.max_q_len == 1 && q.dtype == DType::BF16 && d <= 128 && T <= 65535 &&
-        (ruled || (n_heads / hkv >= kSharedKvMinHeads && (int64_t)T * n_heads * s.max_blocks * c.page_size >= kSharedKvMinTriples))) {
+    // Steps with capped scores, chunks of positions or a bias by distance: this kernel is the decode kernel that has a form
+    // for them, so it takes them all (with few keys it is one launch of one split); a chunk bounds the keys a query walks.
+    if (s.max_q_len == 1 && q.dtype == DType::BF16 && d <= 128 && T <= 65535 &&
+        (ruled || db || (n_heads / hkv >= kSharedKvMinHeads && (int64_t)T * n_heads * s.max_blocks * c.page_size >= kSharedKvMinTriples))) {
         const int max_kv = chunk > 0 ? std::min(chunk, s.max_blocks * c.page_size) : s.max_blocks * c.page_size;
         const int tiles = hkv * ((n_heads / hkv + 15) / 16), groups = (max_kv + 15) / 16;
         const int splits = std::max(1, std::min({(groups + 3) / 4, (2 * sm_count() + T * tiles - 1) / (T * tiles), 64}));
         static auto need = SANDY_KERNEL(attention_decode_shared, sandy_decode_attention_shared_scratch);
-        static auto fn = SANDY_KERNEL(attention_decode_shared, sandy_decode_attention_shared_cap);
+        static auto fn = SANDY_KERNEL(attention_decode_shared, sandy_decode_attention_shared_bias);
         const long long floats = need(T, n_heads, hkv, d, splits);
         float* scratch = floats ? (float*)ws.raw("decode_attention_partial_rows", (size_t)floats * sizeof(float)) : nullptr;
         OpTimer timer(l, "attention, decode (heads as rows)", attn_bytes, attn_flops);
         check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.token_seq, s.positions, out.data, (int)out.ld,
-                 T, n_heads, hkv, d, c.page_size, scale, window, cap, chunk, splits, c.num_pages, sk, og, scratch, l.kernel_status,
-                 l.stream),
+                 T, n_heads, hkv, d, c.page_size, scale, window, cap, chunk, splits, c.num_pages, sk, og, db, n_dist, scratch,
+                 l.kernel_status, l.stream),
               "decode_attention_shared" + shape);
         return;
     }

@@ -138,8 +138,8 @@ struct AttentionExtras {
     const float* out_gate = nullptr;
     float softcap = 0.0f;
     int chunk = 0;
-    // A learned bias by distance: row min(i - j, n_dist - 1) of dist_bias (float32 [n_dist, H]) joins the score of query i
-    // and key j after the scale and the cap.  Null: none.
+    // A learned bias by distance: entry min(i - j, n_dist - 1) of the head's row of dist_bias (float32 [H, n_dist]) joins
+    // the score of query i and key j after the scale and the cap.  Null: none.
     const float* dist_bias = nullptr;
     int n_dist = 0;
 };

@@ -232,8 +232,8 @@ private:
 // inside the root, no gain); the query at position p times 1 + q_pos_coef ln(floor((p + 1) / q_pos_every) + 1);
 //   score(i, j) = (q_i . k_j) scale + rel[bucket(i - j), head],  j <= i
 //   bucket(n)   = n below half = bias_rows / 2, else min(bias_rows - 1, half + floor(ln(n / half) / ln(bias_max / half) (bias_rows - half)))
-// softmax, x += W_o [heads].  The buckets are laid out by distance once, when the part binds: row min(n, bias_max) of a
-// table [bias_max + 1, heads] (every distance from bias_max on falls into the last bucket).
+// softmax, x += W_o [heads].  The buckets are laid out by distance once, when the part binds: entry min(n, bias_max) of a
+// head's row of a table [heads, bias_max + 1] (every distance from bias_max on falls into the last bucket).
 // Keys and values live in pages whose head size is the larger of qk_dim and v_dim rounded up to 16.
 class BiasedAttention : public Mixer {
 public:
@@ -286,7 +286,7 @@ public:
             std::vector<float> by_distance((size_t)(far_ + 1) * H_);
             for (int64_t n = 0; n <= far_; n++) {
                 const int64_t b = bucket(n, rows, far_);
-                for (int h = 0; h < H_; h++) by_distance[(size_t)n * H_ + h] = rel[(size_t)b * H_ + h];
+                for (int h = 0; h < H_; h++) by_distance[(size_t)h * (far_ + 1) + n] = rel[(size_t)b * H_ + h];
             }
             bias_ = floats_to_device(by_distance);
         }

@@ -3,8 +3,8 @@
 // Formula, as the reference computes it (src/core/TensorCalc.cpp:1241-1311):
 //   s[j] = (q . k_j) * scale            for  max(0, pos+1-window) <= j <= pos   (window 0: all)
 //   p[j] = exp(s[j] - max s) / sum exp(s - max s);   o = sum_j p[j] * v_j
-// A learned bias by distance may join a score: row min(pos - j, n_dist - 1) of a table [n_dist, H], added after the
-// scale (and the cap).
+// A learned bias by distance may join a score: entry min(pos - j, n_dist - 1) of the head's row of a table [H, n_dist],
+// added after the scale (and the cap).
 // Two rules some layers add: with softcap > 0 a score becomes softcap * tanh(s / softcap) before the softmax; with
 // chunk > 0 a query at position pos sees only keys of its own chunk, j >= pos - pos % chunk (chunks are counted from
 // position 0 of the request, wherever the step's tokens start).
@@ -144,7 +144,7 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
                 row = (long long)page * rows_per_page + (long long)kvh * page_size + (j % page_size);
                 sc = dot_row<T>(k_cache + row * head_dim, qs, head_dim) * scale;
                 if (softcap > 0.0f) sc = softcap * tanhf(sc / softcap);
-                if (dist_bias) sc += dist_bias[(size_t)min(pos - j, n_dist - 1) * n_heads + h];
+                if (dist_bias) sc += dist_bias[(size_t)h * n_dist + min(pos - j, n_dist - 1)];
             }
         }
         const float m_new = fmaxf(m, warp_max(sc));
@@ -209,8 +209,8 @@ SANDY_API int sandy_kv_append(const void* k_src, const void* v_src, int ld_src,
 // window 0 = every earlier key is visible.  sink: float32 [H] or null: exp(sink[h]) joins the softmax's
 // denominator.  out_gate: float32 [n_tokens, H] or null: a factor on each head's output.
 // out_gate: float32 [n_tokens, H] or null: a factor on each head's output.  softcap 0: scores as they are; chunk 0: no chunks.
-// dist_bias: float32 [n_dist, H] or null: row min(i - j, n_dist - 1) is added to the score of query i and key j (after the
-// scale and the cap), a learned bias by distance.
+// dist_bias: float32 [H, n_dist] or null: entry min(i - j, n_dist - 1) of the head's row is added to the score of query i
+// and key j (after the scale and the cap), a learned bias by distance.
 SANDY_API int sandy_paged_attention_bias(const void* q, int ld_q, const void* k_cache, const void* v_cache,
                                          long long page_stride, const int* block_table, int max_blocks,
                                          const int* token_seq, const int* positions, void* out, int ld_out,

@@ -69,7 +69,7 @@ decode_shared_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __restric
                      const int* __restrict__ token_seq, const int* __restrict__ positions, bf16* __restrict__ out, int ld_out,
                      int n_heads, int n_kv_heads, int page_size, float scale, int window, float softcap, int chunk, int splits,
                      int num_pages, const float* __restrict__ sink, const float* __restrict__ out_gate,
-                     float* __restrict__ scratch, int* __restrict__ status) {
+                     const float* __restrict__ dist_bias, int n_dist, float* __restrict__ scratch, int* __restrict__ status) {
     constexpr int PITCH = D + 8;                       // elements: ldmatrix rows fall on different banks
     constexpr int PIECES = D / 8;                      // 16-byte pieces of a key row
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -162,7 +162,11 @@ decode_shared_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __restric
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const int key = key0 + nt * 8 + tq * 2 + (j & 1);
-                const float sc = softcap > 0.0f ? cap2 * tanh_fast(s[nt][j] * over_cap) : s[nt][j] * s2;
+                float sc = softcap > 0.0f ? cap2 * tanh_fast(s[nt][j] * over_cap) : s[nt][j] * s2;
+                if (dist_bias) {                               // a learned bias by distance, this row's head
+                    const int hd = min(first_head + gq + (j >> 1) * 8, n_heads - 1);
+                    sc = fmaf(__ldg(dist_bias + (size_t)hd * n_dist + min(max(pos - key, 0), n_dist - 1)), LOG2E, sc);
+                }
                 s[nt][j] = key <= pos ? sc : -INFINITY;
             }
         unsigned pa[4];
@@ -299,7 +303,7 @@ template <int D>
 int launch(const bf16* q, int ld_q, const bf16* k, const bf16* v, long long page_stride, const int* block_table, int max_blocks,
            const int* token_seq, const int* positions, bf16* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int page_size,
            float scale, int window, float softcap, int chunk, int splits, int num_pages, const float* sink, const float* out_gate,
-           float* scratch, int* status, cudaStream_t stream) {
+           const float* dist_bias, int n_dist, float* scratch, int* status, cudaStream_t stream) {
     static bool configured = false;
     const size_t smem = smem_bytes<D>(k == v);
     if (!configured) {
@@ -310,8 +314,8 @@ int launch(const bf16* q, int ld_q, const bf16* k, const bf16* v, long long page
     const int group_heads = n_heads / n_kv_heads, tiles = n_kv_heads * ((group_heads + ROWS - 1) / ROWS);
     int code = sandy_launch(decode_shared_kernel<D>, dim3(splits, tiles, n_tokens), dim3(WARPS * 32), smem, stream, q, ld_q, k, v,
                             page_stride, block_table, max_blocks, token_seq, positions, out, ld_out, n_heads, n_kv_heads, page_size,
-                            scale, window, softcap, chunk, splits, num_pages, sink, out_gate, splits > 1 ? scratch : (float*)nullptr,
-                            status);
+                            scale, window, softcap, chunk, splits, num_pages, sink, out_gate, dist_bias, n_dist,
+                            splits > 1 ? scratch : (float*)nullptr, status);
     if (code != SANDY_OK || splits == 1) return code;
     return sandy_launch(decode_shared_merge_kernel<D>, dim3(tiles, n_tokens, (ROWS * D + 127) / 128), dim3(128), 0, stream, (const float*)scratch, splits, out,
                         ld_out, n_heads, n_kv_heads, sink, out_gate);
@@ -331,13 +335,15 @@ SANDY_API long long sandy_decode_attention_shared_scratch(int n_tokens, int n_he
 // step).  sink: float32 [n_heads] or null; out_gate: float32 [n_tokens, n_heads] or null.  scratch: float32, as many
 // floats as sandy_decode_attention_shared_scratch says (may be null with one split).  softcap > 0: a score becomes
 // softcap * tanh(score / softcap); chunk > 0: a query sees only keys j >= pos - pos % chunk.
-SANDY_API int sandy_decode_attention_shared_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+// dist_bias: float32 [n_heads, n_dist] or null: entry min(pos - j, n_dist - 1) of the head's row joins the score of key j.
+SANDY_API int sandy_decode_attention_shared_bias(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
                                             const int* block_table, int max_blocks, const int* token_seq, const int* positions,
                                             void* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                             int page_size, float scale, int window, float softcap, int chunk, int splits,
-                                            int num_pages, const float* sink, const float* out_gate, float* scratch, int* status,
-                                            cudaStream_t stream) {
+                                            int num_pages, const float* sink, const float* out_gate, const float* dist_bias,
+                                            int n_dist, float* scratch, int* status, cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
+    if (dist_bias && n_dist < 1) return SANDY_ERR_ARGUMENT;
     if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out) return SANDY_ERR_ARGUMENT;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0 || window < 0 || splits < 1 || splits > 65535 ||
         n_tokens > 65535 || (splits > 1 && !scratch) || softcap < 0.0f || chunk < 0)
@@ -349,12 +355,24 @@ SANDY_API int sandy_decode_attention_shared_cap(const void* q, int ld_q, const v
     case DD:                                                                                                                        \
         return launch<DD>((const bf16*)q, ld_q, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, block_table, max_blocks,  \
                           token_seq, positions, (bf16*)out, ld_out, n_tokens, n_heads, n_kv_heads, page_size, scale, window, softcap, \
-                          chunk, splits, num_pages, sink, out_gate, scratch, status, stream)
+                          chunk, splits, num_pages, sink, out_gate, dist_bias, n_dist, scratch, status, stream)
     switch (head_dim) {
         SANDY_CASE(16); SANDY_CASE(32); SANDY_CASE(48); SANDY_CASE(64); SANDY_CASE(80); SANDY_CASE(96); SANDY_CASE(112); SANDY_CASE(128);
     }
 #undef SANDY_CASE
     return SANDY_ERR_UNSUPPORTED;
+}
+
+// The same without a bias by distance.
+SANDY_API int sandy_decode_attention_shared_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                            const int* block_table, int max_blocks, const int* token_seq, const int* positions,
+                                            void* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                            int page_size, float scale, int window, float softcap, int chunk, int splits,
+                                            int num_pages, const float* sink, const float* out_gate, float* scratch, int* status,
+                                            cudaStream_t stream) {
+    return sandy_decode_attention_shared_bias(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq, positions, out,
+                                              ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size, scale, window, softcap, chunk,
+                                              splits, num_pages, sink, out_gate, nullptr, 0, scratch, status, stream);
 }
 
 // The same with plain scores and no chunks.

@@ -83,7 +83,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
                          const int* __restrict__ kv_before, bf16* __restrict__ out, int ld_out, int n_heads,
                          int n_kv_heads, int page_size, float scale, int window, float softcap, int chunk, int num_pages,
                          const float* __restrict__ sink, const float* __restrict__ out_gate,
-                         int* __restrict__ status) {
+                         const float* __restrict__ dist_bias, int n_dist, int* __restrict__ status) {
     constexpr int LDS = D + 8;               // row pitch in elements: 16 bytes of padding
     constexpr int CHUNKS = D / 8;            // 16-byte pieces per row
     constexpr int KSTEPS = D / 16;           // k-steps of Q.K^T
@@ -176,6 +176,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
         lo0 = max(lo0, pos0 - pos0 % chunk);
         lo1 = max(lo1, pos1 - pos1 % chunk);
     }
+    const float* bias_h = dist_bias ? dist_bias + (size_t)h * n_dist : nullptr;
     // capped scores: cap * tanh(s * scale / cap), in the softmax's base-2 units
     const float cap_log2 = softcap * 1.4426950408889634f, over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
 
@@ -225,12 +226,24 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
 #pragma unroll
                 for (int e = 0; e < 4; e++) sc[nt][e] = cap_log2 * tanh_fast(sc[nt][e] * over_cap);
             }
+            if (dist_bias) {                                 // a learned bias by distance joins the scaled (or capped) score
+                const int j0 = kt * BN + khalf * BNW + nt * 8 + 2 * t;
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int d0 = min(max(pos0 - j0 - e, 0), n_dist - 1), d1 = min(max(pos1 - j0 - e, 0), n_dist - 1);
+                    const float s0 = softcap > 0.0f ? sc[nt][e] : sc[nt][e] * scale_log2;
+                    const float s1 = softcap > 0.0f ? sc[nt][2 + e] : sc[nt][2 + e] * scale_log2;
+                    sc[nt][e] = fmaf(__ldg(bias_h + d0), 1.4426950408889634f, s0);
+                    sc[nt][2 + e] = fmaf(__ldg(bias_h + d1), 1.4426950408889634f, s1);
+                }
+            }
+            const bool scaled = softcap > 0.0f || dist_bias != nullptr;
             if (whole) {
-                if (softcap <= 0.0f) {
+                if (!scaled) {
 #pragma unroll
                     for (int e = 0; e < 4; e++) sc[nt][e] *= scale_log2;
                 }
-            } else if (softcap > 0.0f) {
+            } else if (scaled) {
                 const int j0 = kt * BN + khalf * BNW + nt * 8 + 2 * t;
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
@@ -361,7 +374,8 @@ template <int D>
 int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
            const int* block_table, int max_blocks, const int* q_start, const int* kv_before, void* out, int ld_out,
            int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int page_size, float scale, int window, float softcap,
-           int chunk, int num_pages, const float* sink, const float* out_gate, int* status, cudaStream_t stream) {
+           int chunk, int num_pages, const float* sink, const float* out_gate, const float* dist_bias, int n_dist, int* status,
+           cudaStream_t stream) {
     constexpr int LDS = D + 8;
     const int smem_two = (BM + 2 * STAGES * BN) * LDS * (int)sizeof(bf16);
     const int smem = k_cache == v_cache ? (BM + STAGES * BN) * LDS * (int)sizeof(bf16) : smem_two;
@@ -375,7 +389,7 @@ int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, lo
     prefill_attention_kernel<D><<<grid, THREADS, smem, stream>>>(
         (const bf16*)q, ld_q, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, block_table, max_blocks, q_start,
         kv_before, (bf16*)out, ld_out, n_heads, n_kv_heads, page_size, scale, window, softcap, chunk, num_pages, sink, out_gate,
-        status);
+        dist_bias, n_dist, status);
     return sandy_launch_status();
 }
 
@@ -383,14 +397,17 @@ int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, lo
 
 // q, out: bfloat16 [n_tokens, H*D]; q_start: int32 [n_seqs + 1], first new token of each request;
 // kv_before: int32 [n_seqs], tokens each request had in the cache before the step;
-// max_q_len: the longest portion (sizes the grid).  Caches, sink, out_gate, softcap and chunk as in attention.cu.
-SANDY_API int sandy_prefill_attention_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+// max_q_len: the longest portion (sizes the grid).  Caches, sink, out_gate, softcap, chunk and dist_bias ([H, n_dist], a
+// learned bias by distance) as in attention.cu.
+SANDY_API int sandy_prefill_attention_bias(const void* q, int ld_q, const void* k_cache, const void* v_cache,
                                       long long page_stride, const int* block_table, int max_blocks,
                                       const int* q_start, const int* kv_before, void* out, int ld_out, int n_seqs,
                                       int max_q_len, int n_heads, int n_kv_heads, int head_dim, int page_size,
                                       float scale, int window, float softcap, int chunk, int num_pages, const float* sink,
-                                      const float* out_gate, int* status, cudaStream_t stream) {
+                                      const float* out_gate, const float* dist_bias, int n_dist, int* status,
+                                      cudaStream_t stream) {
     if (n_seqs == 0 || max_q_len == 0) return SANDY_OK;
+    if (dist_bias && n_dist < 1) return SANDY_ERR_ARGUMENT;
     if (!q || !k_cache || !v_cache || !block_table || !q_start || !kv_before || !out) return SANDY_ERR_ARGUMENT;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || page_size <= 0 || window < 0 || softcap < 0.0f || chunk < 0)
         return SANDY_ERR_UNSUPPORTED;
@@ -404,10 +421,22 @@ SANDY_API int sandy_prefill_attention_cap(const void* q, int ld_q, const void* k
     if (head_dim == DD)                                                                                         \
         return launch<DD>(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, q_start, kv_before,  \
                           out, ld_out, n_seqs, max_q_len, n_heads, n_kv_heads, page_size, scale, window,        \
-                          softcap, chunk, num_pages, sink, out_gate, status, stream)
+                          softcap, chunk, num_pages, sink, out_gate, dist_bias, n_dist, status, stream)
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
 #undef CASE
     return SANDY_ERR_UNSUPPORTED;
+}
+
+// The same without a bias by distance.
+SANDY_API int sandy_prefill_attention_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                      long long page_stride, const int* block_table, int max_blocks,
+                                      const int* q_start, const int* kv_before, void* out, int ld_out, int n_seqs,
+                                      int max_q_len, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                      float scale, int window, float softcap, int chunk, int num_pages, const float* sink,
+                                      const float* out_gate, int* status, cudaStream_t stream) {
+    return sandy_prefill_attention_bias(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, q_start, kv_before, out,
+                                        ld_out, n_seqs, max_q_len, n_heads, n_kv_heads, head_dim, page_size, scale, window,
+                                        softcap, chunk, num_pages, sink, out_gate, nullptr, 0, status, stream);
 }
 
 // The same with plain scores and no chunks.

@@ -116,13 +116,25 @@ int sandy_paged_attention_cap(const void* q, int ld_q, const void* k_cache, cons
                               int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
                               int window, float softcap, int chunk, int num_pages, int dtype, const float* sink,
                               const float* out_gate, int* status, cudaStream_t stream);
-/* ... and with a learned bias by distance: row min(i - j, n_dist - 1) of dist_bias (float32 [n_dist, H]) joins the
-   score of query i and key j after the scale and the cap.  Null: none. */
+/* ... and with a learned bias by distance: entry min(i - j, n_dist - 1) of the head's row of dist_bias (float32
+   [H, n_dist]) joins the score of query i and key j after the scale and the cap.  Null: none. */
 int sandy_paged_attention_bias(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
                                const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
                                int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
                                int window, float softcap, int chunk, int num_pages, int dtype, const float* sink,
                                const float* out_gate, const float* dist_bias, int n_dist, int* status, cudaStream_t stream);
+int sandy_prefill_attention_bias(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                 const int* block_table, int max_blocks, const int* q_start, const int* kv_before, void* out,
+                                 int ld_out, int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int head_dim,
+                                 int page_size, float scale, int window, float softcap, int chunk, int num_pages,
+                                 const float* sink, const float* out_gate, const float* dist_bias, int n_dist, int* status,
+                                 cudaStream_t stream);
+int sandy_decode_attention_shared_bias(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                       const int* block_table, int max_blocks, const int* token_seq, const int* positions,
+                                       void* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                       int page_size, float scale, int window, float softcap, int chunk, int splits,
+                                       int num_pages, const float* sink, const float* out_gate, const float* dist_bias,
+                                       int n_dist, float* scratch, int* status, cudaStream_t stream);
 int sandy_prefill_attention_cap(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
                                 const int* block_table, int max_blocks, const int* q_start, const int* kv_before, void* out,
                                 int ld_out, int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int head_dim,

@@ -303,8 +303,8 @@ def test_the_edges_of_the_bias_table(tmp_path, rows, far, dtype):
     def next_door(w2):
         w2["l0.mix.rel"] = torch.roll(w2["l0.mix.rel"], 1, 0)
 
-    assert rel_error(_without(cfg, w, ids, change_w=next_door), want) > 0.2
-    assert rel_error(_without(cfg, w, ids, change_cfg=lambda c: c["layers"][0]["mixer"].update(bias_max=far * far)), want) > 0.2
+    assert rel_error(_without(cfg, w, ids, change_w=next_door), want) > 0.05
+    assert rel_error(_without(cfg, w, ids, change_cfg=lambda c: c["layers"][0]["mixer"].update(bias_max=far * far)), want) > 0.05
     eng = _engine(path, dtype, max_tokens=512, page_size=16)
     _check(_run_cuts(eng, "r", ids, [n]), (cfg, w), ids, dtype, "bias buckets, whole")
     _check(_run_cuts(eng, "r", ids, [rows // 2, 1, 2, rows, n - rows - rows // 2 - 3]), (cfg, w), ids, dtype, "bias buckets, portions")
