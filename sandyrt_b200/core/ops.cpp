@@ -996,15 +996,22 @@ void streams_step(const Launch& l, Tensor& X, int n_streams, const StreamsStep& 
         throw KernelError("streams_step: the read needs float32 in [S] and gain [width] and h [T, width]");
     if (p.sum_out && (p.sum_out->dtype != DType::F32 || p.sum_out->rows != X.rows || p.sum_out->cols != W))
         throw KernelError("streams_step: the sum is float32 [T, width]");
+    if (p.taps && (!p.in_w || !p.conv_out || p.conv_out->rows != X.rows || p.conv_out->cols != W || p.conv_out->dtype != p.h->dtype ||
+                   !f32(p.taps, W * p.n_taps) || !p.seqs || p.seqs->n_tokens != X.rows ||
+                   (p.n_taps > 1 && (!p.state || p.state->dtype != DType::F32 || p.tail_off + (int64_t)(p.n_taps - 1) * W > p.state->row_elems))))
+        throw KernelError("streams_step: the convolution needs the read, float32 taps [width, n_taps], its output and a float32 state");
     if (left_out("layernorm")) return;
-    static auto fn = SANDY_KERNEL(streams, sandy_streams_step);
+    static auto fn = SANDY_KERNEL(streams, sandy_streams_step_conv);
     OpTimer timer(l, "streams: write + norm", (p.y ? 2.0 : 1.0) * tensor_bytes(&X) + 2 * tensor_bytes(p.y) + tensor_bytes(p.h) + tensor_bytes(p.sum_out), 0);
     check(fn((float*)X.data, (int)X.ld, (int)X.rows, n_streams, (int)W, p.y ? (const float*)p.y->data : nullptr, p.y ? (int)p.y->ld : 0,
              p.y ? (const float*)p.gate->data : nullptr, p.y ? (int)p.gate->ld : 0, p.y ? (const float*)p.gate_bias->data : nullptr,
              p.y ? (const float*)p.mix->data : nullptr, p.y ? (const float*)p.out_w->data : nullptr,
              p.in_w ? (const float*)p.in_w->data : nullptr, p.in_w ? (const float*)p.gain->data : nullptr, p.eps,
              p.in_w ? p.h->data : nullptr, p.in_w ? (int)p.h->ld : 0, p.in_w ? code_of(p.h->dtype) : 0,
-             p.sum_out ? (float*)p.sum_out->data : nullptr, p.sum_out ? (int)p.sum_out->ld : 0, l.stream),
+             p.sum_out ? (float*)p.sum_out->data : nullptr, p.sum_out ? (int)p.sum_out->ld : 0,
+             p.taps ? (const float*)p.taps->data : nullptr, p.taps ? p.n_taps : 0, p.taps && p.state ? (float*)p.state->data : nullptr,
+             p.taps && p.state ? p.state->row_elems : 0, p.tail_off, p.taps ? p.seqs->token_seq : nullptr,
+             p.taps ? p.seqs->seq_slots : nullptr, p.taps ? p.conv_out->data : nullptr, p.taps ? (int)p.conv_out->ld : 0, l.stream),
           "streams_step(S=" + std::to_string(n_streams) + ",width=" + std::to_string(W) + ")");
 }
 

@@ -346,6 +346,14 @@ struct StreamsStep {
     float eps = 0.0f;
     Tensor* h = nullptr;
     Tensor* sum_out = nullptr;
+    // With the read, in a step in which EVERY request brings one token: the short convolution of canon_conv in the same
+    // launch, conv_out = h + conv(h), and the request's tail moved on by the token (canon_conv + conv_tail otherwise).
+    const Tensor* taps = nullptr;            // float32 [width, n_taps]
+    int n_taps = 0;
+    const StateView* state = nullptr;
+    int64_t tail_off = 0;
+    const StepSeqs* seqs = nullptr;
+    Tensor* conv_out = nullptr;
 };
 int streams_max();
 void streams_step(const Launch& l, Tensor& X, int n_streams, const StreamsStep& step);

@@ -134,16 +134,26 @@ public:
         st.gain = &gain_.view;
         st.eps = eps_;
         st.h = &h;
-        ops::streams_step(ctx.launch, X, S_, st);
         Input out;
-        if (taps_) {
-            out.sublayer_in = ws.get("wrap_sublayer_in", T, width_, ctx.compute_dtype);
-            StateView none;
-            const StateView& sv = state ? *state : none;
-            ops::canon_conv(ctx.launch, seqs_of(ctx), h, conv_.view, taps_, sv, offset, out.sublayer_in);
-            if (taps_ > 1) ops::conv_tail(ctx.launch, seqs_of(ctx), h, taps_, sv, offset);
-        } else {
-            out.sublayer_in = h;
+        StateView none;
+        const StateView& sv = state ? *state : none;
+        const ops::StepSeqs seqs = seqs_of(ctx);
+        // a step of single tokens: the convolution and its tail ride in the same launch
+        const bool fused = taps_ && ctx.max_q_len <= 1;
+        if (taps_) out.sublayer_in = ws.get("wrap_sublayer_in", T, width_, ctx.compute_dtype);
+        else out.sublayer_in = h;
+        if (fused) {
+            st.taps = &conv_.view;
+            st.n_taps = taps_;
+            st.state = &sv;
+            st.tail_off = offset;
+            st.seqs = &seqs;
+            st.conv_out = &out.sublayer_in;
+        }
+        ops::streams_step(ctx.launch, X, S_, st);
+        if (taps_ && !fused) {
+            ops::canon_conv(ctx.launch, seqs, h, conv_.view, taps_, sv, offset, out.sublayer_in);
+            if (taps_ > 1) ops::conv_tail(ctx.launch, seqs, h, taps_, sv, offset);
         }
         out.gate = ws.get("wrap_gate", T, width_, DType::F32);
         gate_lin_.run(ctx, nullptr, &h, out.gate, ops::Act::None, nullptr);

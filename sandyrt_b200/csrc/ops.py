@@ -187,10 +187,11 @@ def kv_append(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions)
 
 
 def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *, sink=None, out_gate=None,
-                    n_heads: int, scale: float, window: int = 0, softcap: float = 0.0, chunk: int = 0) -> None:
+                    n_heads: int, scale: float, window: int = 0, softcap: float = 0.0, chunk: int = 0, dist_bias=None) -> None:
     """Causal attention of every token of the step over its request's pages (general kernel).  softcap > 0 presses
     every score into softcap * tanh(score / softcap); chunk > 0 lets a query see the keys of its own chunk of
-    positions only."""
+    positions only; dist_bias (float32 [H, n_dist]) adds entry min(i - j, n_dist - 1) of the head's row to the score of
+    query i and key j."""
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
@@ -203,15 +204,23 @@ def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out,
         raise KernelError("attention: q and out must be [T, H*D] of the cache's dtype")
     _i32(block_table, "block_table"); _i32(token_seq, "token_seq"); _i32(positions, "positions")
     lib = load_library("attention")
-    code = lib.sandy_paged_attention_cap(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
+    code = lib.sandy_paged_attention_bias(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
                                      ctypes.c_longlong(page_stride), _p(block_table),
                                      ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
                                      ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(n_heads),
                                      ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale),
                                      ctypes.c_int(window), ctypes.c_float(softcap), ctypes.c_int(chunk),
                                      ctypes.c_int(num_pages), ctypes.c_int(_dt(q)),
-                                     _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
+                                     _p(sink), _p(out_gate), *_bias_args(dist_bias, n_heads), _p(kernel_status(q.device)), _stream())
     _check(code, f"paged_attention(H={n_heads},Hkv={hkv},D={d})")
+
+
+def _bias_args(dist_bias, n_heads: int):
+    if dist_bias is None:
+        return None, ctypes.c_int(0)
+    if dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[0] != n_heads or not dist_bias.is_contiguous():
+        raise KernelError("attention: a bias by distance is a dense float32 [H, n_dist]")
+    return _p(dist_bias), ctypes.c_int(dist_bias.shape[1])
 
 
 _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
@@ -306,9 +315,9 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
 
 
 def decode_attention_shared(q, k_cache, v_cache, block_table, token_seq, positions, out, *, n_heads: int, scale: float, splits: int = 1,
-                            window: int = 0, sink=None, out_gate=None, softcap: float = 0.0, chunk: int = 0) -> None:
+                            window: int = 0, sink=None, out_gate=None, softcap: float = 0.0, chunk: int = 0, dist_bias=None) -> None:
     """Single-token attention with the query heads of a group as the rows of one tensor-core product (bfloat16, head sizes
-    up to 128); v_cache may be k_cache itself (one plane).  softcap and chunk as in paged_attention."""
+    up to 128); v_cache may be k_cache itself (one plane).  softcap, chunk and dist_bias as in paged_attention."""
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
@@ -316,21 +325,23 @@ def decode_attention_shared(q, k_cache, v_cache, block_table, token_seq, positio
     lib.sandy_decode_attention_shared_scratch.restype = ctypes.c_longlong
     floats = lib.sandy_decode_attention_shared_scratch(ctypes.c_int(T), ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(splits))
     scratch = torch.empty(max(int(floats), 1), dtype=torch.float32, device=q.device)
-    code = lib.sandy_decode_attention_shared_cap(
+    code = lib.sandy_decode_attention_shared_bias(
         _p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache), ctypes.c_longlong(page_stride), _p(block_table),
         ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out), ctypes.c_int(out.stride(0)), ctypes.c_int(T),
         ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window),
-        ctypes.c_float(softcap), ctypes.c_int(chunk), ctypes.c_int(splits), ctypes.c_int(num_pages), _p(sink), _p(out_gate), _p(scratch), _p(kernel_status(q.device)), _stream())
+        ctypes.c_float(softcap), ctypes.c_int(chunk), ctypes.c_int(splits), ctypes.c_int(num_pages), _p(sink), _p(out_gate),
+        *_bias_args(dist_bias, n_heads), _p(scratch), _p(kernel_status(q.device)), _stream())
     _check(code, f"decode_attention_shared(H={n_heads},Hkv={hkv},D={d})")
 
 
 def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out, *, sink=None, out_gate=None, n_heads: int,
-                      max_q_len: int, scale: float, window: int = 0, tc=None, softcap: float = 0.0, chunk: int = 0) -> None:
+                      max_q_len: int, scale: float, window: int = 0, tc=None, softcap: float = 0.0, chunk: int = 0,
+                      dist_bias=None) -> None:
     """Tensor-core attention of prompt portions (bfloat16, head sizes 16..128 in steps of 16).
     q_start: int32 [S+1] first new token of each request; kv_before: int32 [S].
     tc: True asks for the tcgen05 kernel (heads of 64), False for the mma.sync kernel, None
     picks the tcgen05 kernel where it takes the shape.  softcap and chunk as in paged_attention; both kernels
-    have the form for them."""
+    have the form for them.  dist_bias as in paged_attention: the mma.sync kernel alone has the form for it."""
     _cuda(q, k_cache, v_cache, block_table, q_start, kv_before, out, sink, out_gate)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     if q.dtype != torch.bfloat16 or d % 16 != 0 or d > 128:
@@ -350,20 +361,22 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
             ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window),
             ctypes.c_float(softcap), ctypes.c_int(chunk),
             ctypes.c_int(num_pages), _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
-    if tc or (tc is None and d == 64):
+    if dist_bias is not None and tc:
+        raise UnsupportedShape("prefill_attention: the tcgen05 kernel takes no bias by distance")
+    if tc or (tc is None and d == 64 and dist_bias is None):
         code = load_library("attention_prefill_tc").sandy_prefill_attention_tc_cap(*args)
         if code != -1 or tc:
             _check(code, f"prefill_attention_tc(H={n_heads},Hkv={hkv},D={d})")
             return
     lib = load_library("attention_prefill")
-    code = lib.sandy_prefill_attention_cap(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
+    code = lib.sandy_prefill_attention_bias(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
                                        ctypes.c_longlong(page_stride), _p(block_table),
                                        ctypes.c_int(block_table.shape[1]), _p(q_start), _p(kv_before), _p(out),
                                        ctypes.c_int(out.stride(0)), ctypes.c_int(S), ctypes.c_int(max_q_len),
                                        ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps),
                                        ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_float(softcap),
                                        ctypes.c_int(chunk), ctypes.c_int(num_pages),
-                                       _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
+                                       _p(sink), _p(out_gate), *_bias_args(dist_bias, n_heads), _p(kernel_status(q.device)), _stream())
     _check(code, f"prefill_attention(H={n_heads},Hkv={hkv},D={d})")
 
 
@@ -543,6 +556,25 @@ def moe_route_scored(logits, correction, top: int, *, n_groups: int = 1, keep_gr
     return r
 
 
+def moe_route_softmax(logits, correction, top: int, *, weight_scale: float = 1.0, norm_eps: float = 0.0, renormalize: bool = False) -> Routing:
+    """Routing by softmax scores over all experts: the `top` largest scores plus `correction` win, weighted by their plain
+    scores times weight_scale (over their sum + norm_eps only with renormalize).  Then the entries grouped by expert."""
+    _cuda(logits, correction)
+    _f32(logits, "logits"); _f32(correction, "correction")
+    T, E = logits.shape
+    dev = logits.device
+    i32 = lambda n: torch.empty(n, dtype=torch.int32, device=dev)
+    r = Routing(T, E, top, i32(T * top), torch.empty(T * top, dtype=torch.float32, device=dev), i32(E + 1), i32(T * top), i32(T * top))
+    lib = load_library("moe")
+    _check(lib.sandy_moe_route_softmax(_p(logits), ctypes.c_int(logits.stride(0)), _p(correction), ctypes.c_int(T), ctypes.c_int(E),
+                                       ctypes.c_int(top), ctypes.c_float(weight_scale), ctypes.c_float(norm_eps),
+                                       ctypes.c_int(1 if renormalize else 0), _p(r.expert_of), _p(r.weight_of), _stream()),
+           f"moe_route_softmax(E={E},top={top})")
+    _check(lib.sandy_moe_group(_p(r.expert_of), ctypes.c_int(T * top), ctypes.c_int(E), _p(r.group_start), _p(r.entry_of_slot),
+                               _p(r.slot_of_entry), _stream()), "moe_group")
+    return r
+
+
 def expert_product(r: Routing, a, w, out, *, gather: bool, act: str = "none") -> None:
     """out[s] = act(W_e a[row(s)]) for the slots s of every expert e; w [E * N, K]; with `gather` a slot reads its
     token's row of a [T, K], else row s of a [T * top, K].  act "none" | "relu_squared"."""
@@ -592,6 +624,101 @@ def moe_combine(r: Routing, rows, y, *, add: bool) -> None:
                                                  ctypes.c_int(r.n_tokens), ctypes.c_int(r.top), _p(y), ctypes.c_int(y.stride(0)),
                                                  ctypes.c_int(y.shape[1]), ctypes.c_int(1 if add else 0), _stream())
     _check(code, "moe_combine")
+
+
+def moe_combine_identity(r: Routing, n_real: int, h, rows, y, *, add: bool) -> None:
+    """moe_combine where the experts from n_real on hand their input on: such an entry contributes weight * h[t]."""
+    _cuda(rows, y, h)
+    _f32(rows, "rows"); _f32(y, "y")
+    code = load_library("moe").sandy_moe_combine_identity(
+        _p(rows), ctypes.c_int(rows.stride(0)), _p(r.weight_of), _p(r.slot_of_entry), _p(r.expert_of), ctypes.c_int(n_real), _p(h),
+        ctypes.c_int(h.stride(0)), ctypes.c_int(_dt(h)), ctypes.c_int(r.n_tokens), ctypes.c_int(r.top), _p(y), ctypes.c_int(y.stride(0)),
+        ctypes.c_int(y.shape[1]), ctypes.c_int(1 if add else 0), _stream())
+    _check(code, "moe_combine_identity")
+
+
+# ---- a residual stream in several copies; a state-space mixer (streams.cu, ssm_state.cu) ---------------------------
+def streams_step(X, n_streams: int, *, y=None, gate=None, gate_bias=None, mix=None, out_w=None, in_w=None, gain=None, eps: float = 0.0,
+                 h=None, sum_out=None) -> None:
+    """One pass over the streams X (float32 [T, S * width], in place), each part optional and in this order: the write
+    X_t <- sum_s mix[s, t] X_s + out_w[t] * y * sigmoid(gate + gate_bias); sum_out = sum_s X_s; the read
+    h = LayerNorm(sum_s in_w[s] X_s) * gain without an offset."""
+    _cuda(X, y, gate, gate_bias, mix, out_w, in_w, gain, h, sum_out)
+    T, W = X.shape[0], X.shape[1] // n_streams
+    code = load_library("streams").sandy_streams_step(
+        _p(X), ctypes.c_int(X.stride(0)), ctypes.c_int(T), ctypes.c_int(n_streams), ctypes.c_int(W), _p(y),
+        ctypes.c_int(0 if y is None else y.stride(0)), _p(gate), ctypes.c_int(0 if gate is None else gate.stride(0)), _p(gate_bias),
+        _p(mix), _p(out_w), _p(in_w), _p(gain), ctypes.c_float(eps), _p(h), ctypes.c_int(0 if h is None else h.stride(0)),
+        ctypes.c_int(0 if h is None else _dt(h)), _p(sum_out), ctypes.c_int(0 if sum_out is None else sum_out.stride(0)), _stream())
+    _check(code, f"streams_step(S={n_streams},width={W})")
+
+
+def canon_conv(h, taps, state, tail_off: int, token_seq, q_start, seq_slots, out) -> None:
+    """out = h + conv(h): taps float32 [width, n_taps] (the last column the token's own); rows before the step come from
+    the request's tail, float32 [n_taps - 1, width] at tail_off of its row of `state` (float32 [slots, row])."""
+    _cuda(h, taps, state, token_seq, q_start, seq_slots, out)
+    code = load_library("streams").sandy_canon_conv(
+        _p(h), ctypes.c_int(h.stride(0)), _p(taps), ctypes.c_int(taps.shape[1]), _p(state), ctypes.c_longlong(state.stride(0)),
+        ctypes.c_longlong(tail_off), _p(token_seq), _p(q_start), _p(seq_slots), _p(out), ctypes.c_int(out.stride(0)),
+        ctypes.c_int(h.shape[0]), ctypes.c_int(h.shape[1]), ctypes.c_int(_dt(h)), _stream())
+    _check(code, "canon_conv")
+
+
+def conv_tail(rows, n_taps: int, state, tail_off: int, q_start, seq_slots) -> None:
+    """The last n_taps - 1 rows of every request (older ones from the old tail) into its tail in `state`."""
+    _cuda(rows, state, q_start, seq_slots)
+    code = load_library("matrix_state").sandy_conv_tail(
+        _p(rows), ctypes.c_int(rows.stride(0)), ctypes.c_int(_dt(rows)), ctypes.c_int(rows.shape[1]), ctypes.c_int(n_taps), _p(state),
+        ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(tail_off), _p(q_start), _p(seq_slots), ctypes.c_int(seq_slots.numel()), _stream())
+    _check(code, "conv_tail")
+
+
+def embed_bigram(ids, positions, token_seq, q_start, seq_slots, wte, bigram, wpe, state, out, *, mul_prev: int, mul_cur: int, keep: bool) -> None:
+    """out[t] = wte[id] + bigram[(id_before * mul_prev + id * mul_cur) mod buckets] + wpe[pos]; position 0 reads the last row
+    of bigram; `state` int32 [slots, >= 1] holds the token before a step's first one; with keep it takes each token (right
+    for steps of single tokens), otherwise bigram_keep follows."""
+    _cuda(ids, positions, token_seq, q_start, seq_slots, wte, bigram, wpe, state, out)
+    lib = load_library("streams")
+    code = lib.sandy_embed_bigram(
+        _p(ids), _p(positions), _p(token_seq), _p(q_start), _p(seq_slots), _p(wte), _p(bigram), _p(wpe), ctypes.c_int(bigram.shape[0] - 1),
+        ctypes.c_longlong(mul_prev), ctypes.c_longlong(mul_cur), _p(state), ctypes.c_longlong(state.stride(0)), _p(out),
+        ctypes.c_int(out.stride(0)), ctypes.c_int(ids.numel()), ctypes.c_int(wte.shape[0]), ctypes.c_int(0 if wpe is None else wpe.shape[0]),
+        ctypes.c_int(out.shape[1]), ctypes.c_int(_dt(wte)), ctypes.c_int(1 if keep else 0), None, _stream())
+    _check(code, "embed_bigram")
+    if not keep:
+        _check(lib.sandy_bigram_keep(_p(ids), _p(q_start), _p(seq_slots), _p(state), ctypes.c_longlong(state.stride(0)),
+                                     ctypes.c_int(seq_slots.numel()), _stream()), "bigram_keep")
+
+
+def ssm_prepare(proj, taps, conv_bias, dt_raw, dt_bias, a_log, state, tail_off: int, token_seq, q_start, seq_slots, xbc, dta) -> None:
+    """xbc = silu(causal conv(proj) + conv_bias), float32; dta = (softplus(dt_raw + dt_bias), -exp(a_log) * that), float32 [T, 2H]."""
+    _cuda(proj, taps, conv_bias, dt_raw, dt_bias, a_log, state, token_seq, q_start, seq_slots, xbc, dta)
+    code = load_library("ssm_state").sandy_ssm_prepare(
+        _p(proj), ctypes.c_int(proj.stride(0)), ctypes.c_int(_dt(proj)), ctypes.c_int(proj.shape[1]), _p(taps), ctypes.c_int(taps.shape[1]),
+        _p(conv_bias), _p(dt_raw), ctypes.c_int(dt_raw.stride(0)), _p(dt_bias), _p(a_log), ctypes.c_int(dt_raw.shape[1]), _p(state),
+        ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(tail_off), _p(token_seq), _p(q_start), _p(seq_slots), _p(xbc),
+        ctypes.c_int(xbc.stride(0)), _p(dta), ctypes.c_int(proj.shape[0]), _stream())
+    _check(code, "ssm_prepare")
+
+
+def ssm_scan(xbc, dta, d_skip, state, q_start, seq_slots, out, *, n_heads: int, n_groups: int, state_dim: int, v_dim: int) -> None:
+    """The state-space recurrence token by token: S <- exp(dta[1]) S + dt B x^T per head, out = S^T C + d_skip x.  xbc float32
+    [T, H * P + 2 G * N] (x, B, C); `state` float32 [slots, >= H * P * N], a slot's S as [H][P][N]."""
+    _cuda(xbc, dta, d_skip, state, q_start, seq_slots, out)
+    code = load_library("ssm_state").sandy_ssm_scan(
+        _p(xbc), ctypes.c_int(xbc.stride(0)), _p(dta), _p(d_skip), _p(state), ctypes.c_longlong(state.stride(0)), _p(q_start), _p(seq_slots),
+        _p(out), ctypes.c_int(out.stride(0)), ctypes.c_int(seq_slots.numel()), ctypes.c_int(n_heads), ctypes.c_int(n_groups),
+        ctypes.c_int(state_dim), ctypes.c_int(v_dim), _stream())
+    _check(code, f"ssm_scan(H={n_heads},N={state_dim},P={v_dim})")
+
+
+def gated_group_norm(y, z, gain, out, *, groups: int, eps: float) -> None:
+    """out = (y * silu(z)) over its root mean square in `groups` equal parts of a row, times gain; y float32."""
+    _cuda(y, z, gain, out)
+    code = load_library("ssm_state").sandy_gated_group_norm(
+        _p(y), ctypes.c_int(y.stride(0)), _p(z), ctypes.c_int(z.stride(0)), _p(gain), ctypes.c_float(eps), ctypes.c_int(groups), _p(out),
+        ctypes.c_int(out.stride(0)), ctypes.c_int(y.shape[0]), ctypes.c_int(y.shape[1]), ctypes.c_int(_dt(out)), _stream())
+    _check(code, "gated_group_norm")
 
 
 def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, uniform=None, status=None,

@@ -286,6 +286,11 @@ int sandy_streams_step(float* X, int ldX, int n_tokens, int n_streams, int width
                        int ldg, const float* gate_bias, const float* mix, const float* out_w, const float* in_w,
                        const float* gain, float eps, void* h, int ldh, int h_dtype, float* sum_out, int ld_sum,
                        cudaStream_t stream);
+int sandy_streams_step_conv(float* X, int ldX, int n_tokens, int n_streams, int width, const float* y, int ldy, const float* gate,
+                            int ldg, const float* gate_bias, const float* mix, const float* out_w, const float* in_w,
+                            const float* gain, float eps, void* h, int ldh, int h_dtype, float* sum_out, int ld_sum,
+                            const float* taps, int n_taps, float* state, long long state_stride, long long tail_off,
+                            const int* token_seq, const int* seq_slots, void* c, int ldc, cudaStream_t stream);
 int sandy_streams_max(void);
 int sandy_streams_spread(const float* x, int ldx, float* X, int ldX, int n_tokens, int n_streams, int width, cudaStream_t stream);
 int sandy_canon_conv(const void* h, int ldh, const float* taps, int n_taps, const float* state, long long state_stride,

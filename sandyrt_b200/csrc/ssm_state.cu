@@ -6,10 +6,10 @@
 //   sandy_ssm_prepare      per token: the short causal convolution (with bias) and silu of the x, B and C channels, rows
 //                          before the step's first token of a request from the tail in its state; dt = softplus(raw +
 //                          dt_bias) and the decay's logarithm -exp(A_log) dt.  All float32.
-//   sandy_ssm_scan         the recurrence, token by token, each request from its own state.  A block owns 32 columns of
-//                          one head's state for one request; a thread owns one column and every fourth group of four
-//                          rows, so the state update needs no exchange at all and the read-out y one sum over four
-//                          neighbouring lanes.  The tokens' inputs are staged through shared memory eight at a time,
+//   sandy_ssm_scan         the recurrence, token by token, each request from its own state.  A block owns 8 to 32 columns
+//                          of one head's state for one request; 4 to 16 neighbouring threads share a column, each with
+//                          every 4th to 16th group of four rows, so the state update needs no exchange at all and the
+//                          read-out y one sum over those neighbouring lanes.  The tokens' inputs are staged through shared memory eight at a time,
 //                          the next eight in flight meanwhile.  A step may bring any mix of portions and single tokens.
 //   sandy_gated_group_norm out = (y * silu(z)) / rms * gain over `groups` equal parts of a row, the gate BEFORE the norm
 //
@@ -23,8 +23,7 @@
 namespace {
 
 constexpr int MAX_TAPS = 8;
-constexpr int COLS = 32;                       // columns of a head's state per block
-constexpr int THREADS = 128;                   // 32 columns x 4 row slices
+constexpr int THREADS = 128;                   // of the recurrence: columns x the threads that share a column
 constexpr int CHUNK = 8;                       // tokens staged at a time
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
@@ -62,18 +61,21 @@ ssm_prepare_kernel(const T* __restrict__ proj, int ld, int channels, const float
 }
 
 // xbc: float32 [T, ld] rows of (x [H * P], B [G * N], C [G * N]); dta: float32 [T, 2H] (dt, then the decay's logarithm).
-// Q: groups of four rows a thread owns; rows beyond N are zeros.  What a token brings to a block, as it lies in shared
-// memory: B [16 Q], C [16 Q], x [COLS], dt, decay.
-template <int Q>
+// SL: threads that share a column (each owns every SL-th group of four rows); Q: groups of four rows a thread owns; rows
+// beyond N are zeros.  What a token brings to a block, as it lies in shared memory: B [4 Q SL], C [4 Q SL], x [COLS], dt,
+// the decay.
+template <int Q, int SL>
 __global__ void __launch_bounds__(THREADS)
 ssm_scan_kernel(const float* __restrict__ xbc, int ld, const float* __restrict__ dta, const float* __restrict__ d_skip,
                 float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
                 const int* __restrict__ seq_slots, float* __restrict__ out, int ld_out, int n_heads, int n_groups, int N, int P) {
-    constexpr int NP = 16 * Q;
-    constexpr int PER = 2 * NP + COLS + 4;          // dt, the decay's logarithm, and two floats that keep a token's rows 16-byte aligned
+    constexpr int NP = 4 * Q * SL;
+    constexpr int COLS = THREADS / SL;               // columns of a head's state per block
+    constexpr int PER = 2 * NP + COLS + 4;           // dt, the decay's logarithm, and two floats that keep a token's rows 16-byte aligned
+    static_assert(COLS % 4 == 0, "a token's rows stay 16-byte aligned");
     __shared__ __align__(16) float stage[CHUNK * PER];
     const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
-    const int slice = threadIdx.x & 3, col = col0 + (threadIdx.x >> 2);
+    const int slice = threadIdx.x % SL, col = col0 + threadIdx.x / SL;
     const int g = h / (n_heads / n_groups);
     const int t0 = q_start[s], t1 = q_start[s + 1];
     const int inner = n_heads * P;
@@ -85,61 +87,88 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld, const float* __restrict__
     for (int q = 0; q < Q; q++)
 #pragma unroll
         for (int e = 0; e < 4; e++) {
-            const int n = 16 * q + 4 * slice + e;
+            const int n = 4 * (q * SL + slice) + e;
             st[q][e] = (col < P && n < N) ? S[n] : 0.0f;
         }
-    constexpr int NL = (CHUNK * PER + THREADS - 1) / THREADS;
-    float pre[NL];
+    // What this thread copies for every token: elements tid, tid + THREADS, ... of the token's PER floats.  Where each
+    // comes from is the same for every token, so it is worked out once: an offset into the token's row of xbc, or one of
+    // the two gate numbers, or nothing (zeros: rows beyond N, columns beyond P, padding).
+    constexpr int NY = (PER + THREADS - 1) / THREADS;
+    int src[NY];
+#pragma unroll
+    for (int y = 0; y < NY; y++) {
+        const int e = threadIdx.x + y * THREADS;
+        int o = -1;
+        if (e < NP) o = e < N ? inner + g * N + e : -1;
+        else if (e < 2 * NP) o = e - NP < N ? inner + n_groups * N + g * N + (e - NP) : -1;
+        else if (e < 2 * NP + COLS) o = col0 + e - 2 * NP < P ? h * P + col0 + e - 2 * NP : -1;
+        else if (e == 2 * NP + COLS) o = -2;
+        else if (e == 2 * NP + COLS + 1) o = -3;
+        src[y] = o;
+    }
+    float pre[CHUNK][NY];
     auto fetch = [&](int tc) {
         const int n_tok = min(CHUNK, t1 - tc);
 #pragma unroll
-        for (int x = 0; x < NL; x++) {
-            const int f = threadIdx.x + x * THREADS;
-            const int tok = f / PER, j = f % PER;
-            float v = 0.0f;
-            if (tok < n_tok) {
-                const float* row = xbc + (size_t)(tc + tok) * ld;
-                if (j < NP) v = j < N ? row[inner + g * N + j] : 0.0f;
-                else if (j < 2 * NP) v = j - NP < N ? row[inner + n_groups * N + g * N + (j - NP)] : 0.0f;
-                else if (j < 2 * NP + COLS) v = col0 + j - 2 * NP < P ? row[h * P + col0 + j - 2 * NP] : 0.0f;
-                else if (j < 2 * NP + COLS + 2) v = dta[(size_t)(tc + tok) * 2 * n_heads + (j - 2 * NP - COLS) * n_heads + h];
+        for (int tok = 0; tok < CHUNK; tok++) {
+            const float* row = xbc + (size_t)(tc + tok) * ld;
+            const float* gates = dta + (size_t)(tc + tok) * 2 * n_heads + h;
+#pragma unroll
+            for (int y = 0; y < NY; y++) {
+                float v = 0.0f;
+                if (tok < n_tok) {
+                    if (src[y] >= 0) v = row[src[y]];
+                    else if (src[y] == -2) v = gates[0];
+                    else if (src[y] == -3) v = gates[n_heads];
+                }
+                pre[tok][y] = v;
             }
-            pre[x] = v;
         }
     };
     if (t0 < t1) fetch(t0);
     for (int tc = t0; tc < t1; tc += CHUNK) {
         __syncthreads();
 #pragma unroll
-        for (int x = 0; x < NL; x++) {
-            const int f = threadIdx.x + x * THREADS;
-            if (f < CHUNK * PER) stage[f] = pre[x];
-        }
+        for (int tok = 0; tok < CHUNK; tok++)
+#pragma unroll
+            for (int y = 0; y < NY; y++) {
+                const int e = threadIdx.x + y * THREADS;
+                if (e < PER) stage[tok * PER + e] = e == 2 * NP + COLS + 1 ? expf(pre[tok][y]) : pre[tok][y];      // the decay itself
+            }
         __syncthreads();
         if (tc + CHUNK < t1) fetch(tc + CHUNK);
         const int n_tok = min(CHUNK, t1 - tc);
-        for (int tok = 0; tok < n_tok; tok++) {
+        auto token = [&](int tok) {
             const float* in = stage + tok * PER;
-            const float xv = in[2 * NP + (threadIdx.x >> 2)];
-            const float dt = in[2 * NP + COLS], decay = expf(in[2 * NP + COLS + 1]);
+            const float xv = in[2 * NP + threadIdx.x / SL];
+            const float dt = in[2 * NP + COLS], decay = in[2 * NP + COLS + 1];
             const float dtx = dt * xv;
-            float y = 0.0f;
+            float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;      // four chains: a token's read-out is not one long chain of additions
 #pragma unroll
             for (int q = 0; q < Q; q++) {
-                const float4 b = *reinterpret_cast<const float4*>(in + 16 * q + 4 * slice);
-                const float4 c = *reinterpret_cast<const float4*>(in + NP + 16 * q + 4 * slice);
+                const float4 b = *reinterpret_cast<const float4*>(in + 4 * (q * SL + slice));
+                const float4 c = *reinterpret_cast<const float4*>(in + NP + 4 * (q * SL + slice));
                 st[q][0] = fmaf(b.x, dtx, decay * st[q][0]);
                 st[q][1] = fmaf(b.y, dtx, decay * st[q][1]);
                 st[q][2] = fmaf(b.z, dtx, decay * st[q][2]);
                 st[q][3] = fmaf(b.w, dtx, decay * st[q][3]);
-                y = fmaf(st[q][0], c.x, y);
-                y = fmaf(st[q][1], c.y, y);
-                y = fmaf(st[q][2], c.z, y);
-                y = fmaf(st[q][3], c.w, y);
+                y0 = fmaf(st[q][0], c.x, y0);
+                y1 = fmaf(st[q][1], c.y, y1);
+                y2 = fmaf(st[q][2], c.z, y2);
+                y3 = fmaf(st[q][3], c.w, y3);
             }
-            y += __shfl_xor_sync(0xffffffffu, y, 1);
-            y += __shfl_xor_sync(0xffffffffu, y, 2);
+            float y = (y0 + y1) + (y2 + y3);
+#pragma unroll
+            for (int o = 1; o < SL; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);      // the SL threads of a column are neighbours
             if (slice == 0 && col < P) out[(size_t)(tc + tok) * ld_out + h * P + col] = fmaf(skip, xv, y);
+        };
+        // Only the state's update ties a token to the one before: with the eight tokens written out, a token's loads and
+        // the sum over a column's threads run under its neighbours' arithmetic.
+        if (n_tok == CHUNK) {
+#pragma unroll
+            for (int tok = 0; tok < CHUNK; tok++) token(tok);
+        } else {
+            for (int tok = 0; tok < n_tok; tok++) token(tok);
         }
     }
     pdl_launch_dependents();
@@ -148,7 +177,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld, const float* __restrict__
         for (int q = 0; q < Q; q++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const int n = 16 * q + 4 * slice + e;
+                const int n = 4 * (q * SL + slice) + e;
                 if (n < N) S[n] = st[q][e];
             }
     }
@@ -212,16 +241,21 @@ SANDY_API int sandy_ssm_scan(const float* xbc, int ld, const float* dta, const f
     if (!xbc || !dta || !state || !q_start || !seq_slots || !out) return SANDY_ERR_ARGUMENT;
     if (n_heads < 1 || n_groups < 1 || n_heads % n_groups || state_dim < 1 || state_dim > 256 || v_dim < 1)
         return SANDY_ERR_UNSUPPORTED;
-    const dim3 grid(n_seqs, n_heads, (v_dim + COLS - 1) / COLS);
-    if (grid.y > 65535 || grid.z > 65535) return SANDY_ERR_UNSUPPORTED;
-#define SCAN(Q)                                                                                                              \
-    return sandy_launch(ssm_scan_kernel<Q>, grid, dim3(THREADS), 0, stream, xbc, ld, dta, d_skip, state, state_stride, q_start, \
-                        seq_slots, out, ld_out, n_heads, n_groups, state_dim, v_dim)
-    if (state_dim <= 16) SCAN(1);
-    if (state_dim <= 32) SCAN(2);
-    if (state_dim <= 64) SCAN(4);
-    if (state_dim <= 128) SCAN(8);
-    SCAN(16);
+#define SCAN(Q, SL)                                                                                                          \
+    do {                                                                                                                     \
+        const dim3 grid(n_seqs, n_heads, (v_dim + THREADS / SL - 1) / (THREADS / SL));                                       \
+        if (grid.y > 65535 || grid.z > 65535) return SANDY_ERR_UNSUPPORTED;                                                  \
+        return sandy_launch(ssm_scan_kernel<Q, SL>, grid, dim3(THREADS), 0, stream, xbc, ld, dta, d_skip, state, state_stride, \
+                            q_start, seq_slots, out, ld_out, n_heads, n_groups, state_dim, v_dim);                           \
+    } while (0)
+    // a thread owns at most sixteen rows of its column (eight up to a state of 128): the tokens of a request come one
+    // after another, so what a token costs is the length of a thread's chain of instructions, and the more threads
+    // share a column the shorter it is
+    if (state_dim <= 16) SCAN(1, 4);
+    if (state_dim <= 32) SCAN(1, 8);
+    if (state_dim <= 64) SCAN(1, 16);
+    if (state_dim <= 128) SCAN(2, 16);
+    SCAN(4, 16);
 #undef SCAN
 }
 

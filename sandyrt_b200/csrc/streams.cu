@@ -11,7 +11,8 @@
 //   sandy_streams_step     for every token, in this order and each part optional: the write of one sublayer's result
 //                          into the streams, the read (and norm) for the next sublayer, and the plain sum of the streams
 //                          (what the model's final norm reads).  One block a token; a token's S rows stay in registers
-//                          between the parts, so a write followed by a read costs one pass over the streams.
+//                          between the parts, so a write followed by a read costs one pass over the streams.  In a step of
+//                          single tokens the same launch also runs the short convolution below and moves its tail on.
 //   sandy_streams_spread   X_s = x for every s: the embedding's output enters all streams
 //   sandy_canon_conv       c[t] = h[t] + sum_k taps[:, k] h[t - n + 1 + k]: a short causal convolution over time on every
 //                          channel, added to its own input; rows before the step's first token of a request come from
@@ -38,7 +39,9 @@ streams_step_kernel(float* __restrict__ X, int ldX, int n_streams, int width,
                     const float* __restrict__ y, int ldy, const float* __restrict__ gate, int ldg,
                     const float* __restrict__ gate_bias, const float* __restrict__ mix, const float* __restrict__ out_w,
                     const float* __restrict__ in_w, const float* __restrict__ gain, float eps, T* __restrict__ h, int ldh,
-                    float* __restrict__ sum_out, int ld_sum) {
+                    float* __restrict__ sum_out, int ld_sum, const float* __restrict__ taps, int n_taps, float* __restrict__ state,
+                    long long state_stride, long long tail_off, const int* __restrict__ token_seq,
+                    const int* __restrict__ seq_slots, T* __restrict__ c, int ldc) {
     __shared__ float scratch[32];
     __shared__ float coef[S_MAX * S_MAX + 2 * S_MAX];
     const int t = blockIdx.x;
@@ -120,9 +123,26 @@ streams_step_kernel(float* __restrict__ X, int ldX, int n_streams, int width,
         }
     }
     const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+    // A step of single tokens runs the short convolution here too: c = h + conv(h) from the request's tail, which then
+    // moves on by this token (a thread owns its channels of the tail: nobody else reads or writes them in this step).
+    float* tail = taps && n_taps > 1 ? state + (long long)seq_slots[token_seq[t]] * state_stride + tail_off : nullptr;
     for (int r = 0; r < rounds; r++) {
         const int j = threadIdx.x + r * THREADS;
-        if (j < width) h[(size_t)t * ldh + j] = from_f32<T>((u_at(r, j) - mean) * rstd * gain[j]);
+        if (j < width) {
+            const T rounded = from_f32<T>((u_at(r, j) - mean) * rstd * gain[j]);
+            h[(size_t)t * ldh + j] = rounded;
+            if (taps) {
+                const float own = to_f32(rounded);
+                float a = taps[(size_t)j * n_taps + n_taps - 1] * own;
+                for (int k = 0; k + 1 < n_taps; k++) {
+                    const float x = tail[(size_t)k * width + j];
+                    a = fmaf(taps[(size_t)j * n_taps + k], x, a);
+                    if (k > 0) tail[(size_t)(k - 1) * width + j] = x;
+                }
+                if (n_taps > 1) tail[(size_t)(n_taps - 2) * width + j] = own;
+                c[(size_t)t * ldc + j] = from_f32<T>(own + a);
+            }
+        }
     }
 }
 
@@ -144,14 +164,13 @@ __global__ void __launch_bounds__(THREADS)
 canon_conv_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ taps, int n_taps, const float* __restrict__ state,
                   long long state_stride, long long tail_off, const int* __restrict__ token_seq, const int* __restrict__ q_start,
                   const int* __restrict__ seq_slots, T* __restrict__ c, int ldc, int n_tokens, int width) {
+    const int t = blockIdx.x;                        // a block a token
+    const int s = token_seq[t];
+    const int i_in_step = t - q_start[s];
+    const float* tail = state + (long long)seq_slots[s] * state_stride + tail_off;
     pdl_wait();
     pdl_launch_dependents();
-    const long long n = (long long)n_tokens * width;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        const int t = (int)(i / width), j = (int)(i % width);
-        const int s = token_seq[t];
-        const int i_in_step = t - q_start[s];
-        const float* tail = state + (long long)seq_slots[s] * state_stride + tail_off;
+    for (int j = threadIdx.x; j < width; j += THREADS) {
         const float own = to_f32(h[(size_t)t * ldh + j]);
         float a = 0.0f;
         for (int k = 0; k < n_taps; k++) {
@@ -162,6 +181,7 @@ canon_conv_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ ta
         }
         c[(size_t)t * ldc + j] = from_f32<T>(own + a);
     }
+    (void)n_tokens;
 }
 
 template <typename T>
@@ -216,10 +236,12 @@ inline unsigned blocks_for(long long n) {
 template <typename T>
 int launch_step(float* X, int ldX, int n_tokens, int S, int width, const float* y, int ldy, const float* gate, int ldg,
                 const float* gate_bias, const float* mix, const float* out_w, const float* in_w, const float* gain, float eps,
-                T* h, int ldh, float* sum_out, int ld_sum, cudaStream_t stream) {
+                T* h, int ldh, float* sum_out, int ld_sum, const float* taps, int n_taps, float* state, long long state_stride,
+                long long tail_off, const int* token_seq, const int* seq_slots, T* c, int ldc, cudaStream_t stream) {
 #define STEP(SM, PER)                                                                                                        \
     return sandy_launch(streams_step_kernel<T, SM, PER>, dim3(n_tokens), dim3(THREADS), 0, stream, X, ldX, S, width, y, ldy, \
-                        gate, ldg, gate_bias, mix, out_w, in_w, gain, eps, h, ldh, sum_out, ld_sum)
+                        gate, ldg, gate_bias, mix, out_w, in_w, gain, eps, h, ldh, sum_out, ld_sum, taps, n_taps, state,      \
+                        state_stride, tail_off, token_seq, seq_slots, c, ldc)
     if (S <= 2) {
         if (width <= 2 * THREADS) STEP(2, 2);
         if (width <= 4 * THREADS) STEP(2, 4);
@@ -243,20 +265,37 @@ int launch_step(float* X, int ldX, int n_tokens, int S, int width, const float* 
 //   is y * sigmoid(gate + gate_bias)), mix float32 [n_streams, n_streams] indexed [from, to], out_w float32 [n_streams].
 // Read (in_w != null): in_w float32 [n_streams], gain float32 [width], eps; h [n_tokens, width] of h_dtype.
 // Sum (sum_out != null): float32 [n_tokens, width] = the sum of the streams (after the write).
+// Convolution (taps != null, only with the read and ONLY in a step in which every request brings one token): c = h + conv(h)
+//   as sandy_canon_conv gives it, [n_tokens, width] of h_dtype, and the request's tail (float32 [n_taps - 1][width] at tail_off
+//   of its row of `state`) moved on by the token.
+SANDY_API int sandy_streams_step_conv(float* X, int ldX, int n_tokens, int n_streams, int width, const float* y, int ldy,
+                                      const float* gate, int ldg, const float* gate_bias, const float* mix, const float* out_w,
+                                      const float* in_w, const float* gain, float eps, void* h, int ldh, int h_dtype,
+                                      float* sum_out, int ld_sum, const float* taps, int n_taps, float* state,
+                                      long long state_stride, long long tail_off, const int* token_seq, const int* seq_slots,
+                                      void* c, int ldc, cudaStream_t stream) {
+    if (n_tokens == 0 || width == 0) return SANDY_OK;
+    if (!X || (y && (!gate || !gate_bias || !mix || !out_w)) || (in_w && (!gain || !h))) return SANDY_ERR_ARGUMENT;
+    if (taps && (!in_w || !c || n_taps < 1 || n_taps > MAX_TAPS || (n_taps > 1 && (!state || !token_seq || !seq_slots)))) return SANDY_ERR_ARGUMENT;
+    if (n_streams < 1 || n_streams > MAX_STREAMS) return SANDY_ERR_UNSUPPORTED;
+    if (h_dtype == SANDY_F32)
+        return launch_step<float>(X, ldX, n_tokens, n_streams, width, y, ldy, gate, ldg, gate_bias, mix, out_w, in_w, gain, eps,
+                                  (float*)h, ldh, sum_out, ld_sum, taps, n_taps, state, state_stride, tail_off, token_seq, seq_slots,
+                                  (float*)c, ldc, stream);
+    if (h_dtype == SANDY_BF16)
+        return launch_step<bf16>(X, ldX, n_tokens, n_streams, width, y, ldy, gate, ldg, gate_bias, mix, out_w, in_w, gain, eps,
+                                 (bf16*)h, ldh, sum_out, ld_sum, taps, n_taps, state, state_stride, tail_off, token_seq, seq_slots,
+                                 (bf16*)c, ldc, stream);
+    return SANDY_ERR_UNSUPPORTED;
+}
+
+// The same without the convolution.
 SANDY_API int sandy_streams_step(float* X, int ldX, int n_tokens, int n_streams, int width, const float* y, int ldy,
                                  const float* gate, int ldg, const float* gate_bias, const float* mix, const float* out_w,
                                  const float* in_w, const float* gain, float eps, void* h, int ldh, int h_dtype, float* sum_out,
                                  int ld_sum, cudaStream_t stream) {
-    if (n_tokens == 0 || width == 0) return SANDY_OK;
-    if (!X || (y && (!gate || !gate_bias || !mix || !out_w)) || (in_w && (!gain || !h))) return SANDY_ERR_ARGUMENT;
-    if (n_streams < 1 || n_streams > MAX_STREAMS) return SANDY_ERR_UNSUPPORTED;
-    if (h_dtype == SANDY_F32)
-        return launch_step<float>(X, ldX, n_tokens, n_streams, width, y, ldy, gate, ldg, gate_bias, mix, out_w, in_w, gain, eps,
-                                  (float*)h, ldh, sum_out, ld_sum, stream);
-    if (h_dtype == SANDY_BF16)
-        return launch_step<bf16>(X, ldX, n_tokens, n_streams, width, y, ldy, gate, ldg, gate_bias, mix, out_w, in_w, gain, eps,
-                                 (bf16*)h, ldh, sum_out, ld_sum, stream);
-    return SANDY_ERR_UNSUPPORTED;
+    return sandy_streams_step_conv(X, ldX, n_tokens, n_streams, width, y, ldy, gate, ldg, gate_bias, mix, out_w, in_w, gain, eps, h, ldh,
+                                   h_dtype, sum_out, ld_sum, nullptr, 0, nullptr, 0, 0, nullptr, nullptr, nullptr, 0, stream);
 }
 
 SANDY_API int sandy_streams_max(void) { return MAX_STREAMS; }
@@ -276,7 +315,7 @@ SANDY_API int sandy_canon_conv(const void* h, int ldh, const float* taps, int n_
     if (n_tokens == 0 || width == 0) return SANDY_OK;
     if (!h || !taps || !c || !token_seq || !q_start || !seq_slots || (n_taps > 1 && !state) || h == c) return SANDY_ERR_ARGUMENT;
     if (n_taps < 1 || n_taps > MAX_TAPS) return SANDY_ERR_UNSUPPORTED;
-    const unsigned grid = blocks_for((long long)n_tokens * width);
+    const unsigned grid = (unsigned)n_tokens;
     if (dtype == SANDY_F32)
         return sandy_launch(canon_conv_kernel<float>, dim3(grid), dim3(THREADS), 0, stream, (const float*)h, ldh, taps, n_taps, state,
                             state_stride, tail_off, token_seq, q_start, seq_slots, (float*)c, ldc, n_tokens, width);
