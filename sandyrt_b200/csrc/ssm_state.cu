@@ -6,11 +6,11 @@
 //   sandy_ssm_prepare      per token: the short causal convolution (with bias) and silu of the x, B and C channels, rows
 //                          before the step's first token of a request from the tail in its state; dt = softplus(raw +
 //                          dt_bias) and the decay's logarithm -exp(A_log) dt.  All float32.
-//   sandy_ssm_scan         the recurrence, token by token, each request from its own state.  A block owns 8 to 32 columns
-//                          of one head's state for one request; 4 to 16 neighbouring threads share a column, each with
-//                          every 4th to 16th group of four rows, so the state update needs no exchange at all and the
-//                          read-out y one sum over those neighbouring lanes.  The tokens' inputs are staged through shared memory eight at a time,
-//                          the next eight in flight meanwhile.  A step may bring any mix of portions and single tokens.
+//   sandy_ssm_scan         the recurrence, token by token, each request from its own state.  A block owns 4 to 32 columns
+//                          of one head's state for one request; 4 to 32 neighbouring threads share a column, each with
+//                          every 4th to 32nd group of four rows, so the state update needs no exchange at all and the
+//                          read-out y one sum over those neighbouring lanes.  The tokens' inputs reach shared memory eight at a
+//                          time by asynchronous copies, the next eight on their way meanwhile.  A step may bring any mix of portions and single tokens.
 //   sandy_gated_group_norm out = (y * silu(z)) / rms * gain over `groups` equal parts of a row, the gate BEFORE the norm
 //
 // The state of a slot is S [H][P][N] (a column's rows are consecutive floats).  Everything is float32 arithmetic whatever
@@ -63,17 +63,18 @@ ssm_prepare_kernel(const T* __restrict__ proj, int ld, int channels, const float
 // xbc: float32 [T, ld] rows of (x [H * P], B [G * N], C [G * N]); dta: float32 [T, 2H] (dt, then the decay's logarithm).
 // SL: threads that share a column (each owns every SL-th group of four rows); Q: groups of four rows a thread owns; rows
 // beyond N are zeros.  What a token brings to a block, as it lies in shared memory: B [4 Q SL], C [4 Q SL], x [COLS], dt,
-// the decay.
+// the decay's logarithm.
 template <int Q, int SL>
 __global__ void __launch_bounds__(THREADS)
 ssm_scan_kernel(const float* __restrict__ xbc, int ld, const float* __restrict__ dta, const float* __restrict__ d_skip,
                 float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
-                const int* __restrict__ seq_slots, float* __restrict__ out, int ld_out, int n_heads, int n_groups, int N, int P) {
+                const int* __restrict__ seq_slots, float* __restrict__ out, int ld_out, int n_heads, int n_groups, int N, int P,
+                int wide) {
     constexpr int NP = 4 * Q * SL;
     constexpr int COLS = THREADS / SL;               // columns of a head's state per block
     constexpr int PER = 2 * NP + COLS + 4;           // dt, the decay's logarithm, and two floats that keep a token's rows 16-byte aligned
     static_assert(COLS % 4 == 0, "a token's rows stay 16-byte aligned");
-    __shared__ __align__(16) float stage[CHUNK * PER];
+    __shared__ __align__(16) float stage[2][CHUNK * PER];
     const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
     const int slice = threadIdx.x % SL, col = col0 + threadIdx.x / SL;
     const int g = h / (n_heads / n_groups);
@@ -81,15 +82,6 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld, const float* __restrict__
     const int inner = n_heads * P;
     const float skip = d_skip ? d_skip[h] : 0.0f;
     float* S = state + (long long)seq_slots[s] * state_stride + ((long long)h * P + col) * N;
-    pdl_wait();
-    float st[Q][4];
-#pragma unroll
-    for (int q = 0; q < Q; q++)
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const int n = 4 * (q * SL + slice) + e;
-            st[q][e] = (col < P && n < N) ? S[n] : 0.0f;
-        }
     // What this thread copies for every token: elements tid, tid + THREADS, ... of the token's PER floats.  Where each
     // comes from is the same for every token, so it is worked out once: an offset into the token's row of xbc, or one of
     // the two gate numbers, or nothing (zeros: rows beyond N, columns beyond P, padding).
@@ -106,42 +98,86 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld, const float* __restrict__
         else if (e == 2 * NP + COLS + 1) o = -3;
         src[y] = o;
     }
-    float pre[CHUNK][NY];
-    auto fetch = [&](int tc) {
+    pdl_wait();
+    float st[Q][4];
+#pragma unroll
+    for (int q = 0; q < Q; q++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int n = 4 * (q * SL + slice) + e;
+            st[q][e] = (col < P && n < N) ? S[n] : 0.0f;
+        }
+    // Eight tokens' inputs go from global to shared memory by asynchronous copies (zeros where there is nothing), into
+    // the buffer that is not being read: they are on their way while the eight before are computed.  Where every row
+    // starts on a 16-byte boundary (`wide`) B, C and x travel sixteen bytes a copy, else four.
+    constexpr int NV = (PER / 4 + THREADS - 1) / THREADS;
+    int vsrc[NV];
+#pragma unroll
+    for (int y = 0; y < NV; y++) {
+        const int e = 4 * (threadIdx.x + y * THREADS);       // first float of this thread's piece
+        int o = -1;
+        if (e < NP) o = e < N ? inner + g * N + e : -1;
+        else if (e < 2 * NP) o = e - NP < N ? inner + n_groups * N + g * N + (e - NP) : -1;
+        else if (e < 2 * NP + COLS) o = col0 + e - 2 * NP < P ? h * P + col0 + e - 2 * NP : -1;
+        else if (e == 2 * NP + COLS) o = -2;                 // dt and the decay's logarithm: two copies of four bytes
+        vsrc[y] = o;
+    }
+    auto fetch = [&](int tc, int buf) {
         const int n_tok = min(CHUNK, t1 - tc);
+        if (wide) {
 #pragma unroll
-        for (int tok = 0; tok < CHUNK; tok++) {
-            const float* row = xbc + (size_t)(tc + tok) * ld;
-            const float* gates = dta + (size_t)(tc + tok) * 2 * n_heads + h;
+            for (int tok = 0; tok < CHUNK; tok++) {
+                const float* row = xbc + (size_t)(tc + tok) * ld;
 #pragma unroll
-            for (int y = 0; y < NY; y++) {
-                float v = 0.0f;
-                if (tok < n_tok) {
-                    if (src[y] >= 0) v = row[src[y]];
-                    else if (src[y] == -2) v = gates[0];
-                    else if (src[y] == -3) v = gates[n_heads];
+                for (int y = 0; y < NV; y++) {
+                    const int e = 4 * (threadIdx.x + y * THREADS);
+                    if (e >= PER) continue;
+                    const unsigned dst = (unsigned)__cvta_generic_to_shared(&stage[buf][tok * PER + e]);
+                    if (vsrc[y] == -2) {
+                        const float* gates = dta + (size_t)(tc + tok) * 2 * n_heads + h;
+                        const int bytes = tok < n_tok ? 4 : 0;
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(gates), "r"(bytes) : "memory");
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst + 4), "l"(gates + n_heads), "r"(bytes) : "memory");
+                    } else {
+                        const bool real = tok < n_tok && vsrc[y] >= 0;
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(real ? row + vsrc[y] : xbc), "r"(real ? 16 : 0) : "memory");
+                    }
                 }
-                pre[tok][y] = v;
+            }
+        } else {
+#pragma unroll
+            for (int tok = 0; tok < CHUNK; tok++) {
+                const float* row = xbc + (size_t)(tc + tok) * ld;
+                const float* gates = dta + (size_t)(tc + tok) * 2 * n_heads + h;
+#pragma unroll
+                for (int y = 0; y < NY; y++) {
+                    const int e = threadIdx.x + y * THREADS;
+                    if (e < PER) {
+                        const bool real = tok < n_tok && src[y] != -1;
+                        const float* from = !real ? xbc : src[y] >= 0 ? row + src[y] : src[y] == -2 ? gates : gates + n_heads;
+                        const unsigned dst = (unsigned)__cvta_generic_to_shared(&stage[buf][tok * PER + e]);
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(from), "r"(real ? 4 : 0) : "memory");
+                    }
+                }
             }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    if (t0 < t1) fetch(t0);
-    for (int tc = t0; tc < t1; tc += CHUNK) {
+    if (t0 < t1) fetch(t0, 0);
+    int buf = 0;
+    for (int tc = t0; tc < t1; tc += CHUNK, buf ^= 1) {
+        if (tc + CHUNK < t1) {
+            fetch(tc + CHUNK, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
         __syncthreads();
-#pragma unroll
-        for (int tok = 0; tok < CHUNK; tok++)
-#pragma unroll
-            for (int y = 0; y < NY; y++) {
-                const int e = threadIdx.x + y * THREADS;
-                if (e < PER) stage[tok * PER + e] = e == 2 * NP + COLS + 1 ? expf(pre[tok][y]) : pre[tok][y];      // the decay itself
-            }
-        __syncthreads();
-        if (tc + CHUNK < t1) fetch(tc + CHUNK);
         const int n_tok = min(CHUNK, t1 - tc);
-        auto token = [&](int tok) {
-            const float* in = stage + tok * PER;
+        for (int tok = 0; tok < n_tok; tok++) {
+            const float* in = stage[buf] + tok * PER;
             const float xv = in[2 * NP + threadIdx.x / SL];
-            const float dt = in[2 * NP + COLS], decay = in[2 * NP + COLS + 1];
+            const float dt = in[2 * NP + COLS], decay = expf(in[2 * NP + COLS + 1]);
             const float dtx = dt * xv;
             float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;      // four chains: a token's read-out is not one long chain of additions
 #pragma unroll
@@ -161,15 +197,8 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld, const float* __restrict__
 #pragma unroll
             for (int o = 1; o < SL; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);      // the SL threads of a column are neighbours
             if (slice == 0 && col < P) out[(size_t)(tc + tok) * ld_out + h * P + col] = fmaf(skip, xv, y);
-        };
-        // Only the state's update ties a token to the one before: with the eight tokens written out, a token's loads and
-        // the sum over a column's threads run under its neighbours' arithmetic.
-        if (n_tok == CHUNK) {
-#pragma unroll
-            for (int tok = 0; tok < CHUNK; tok++) token(tok);
-        } else {
-            for (int tok = 0; tok < n_tok; tok++) token(tok);
         }
+        __syncthreads();             // everyone is done with this buffer before the copies after next land in it
     }
     pdl_launch_dependents();
     if (t0 < t1 && col < P) {
@@ -246,16 +275,18 @@ SANDY_API int sandy_ssm_scan(const float* xbc, int ld, const float* dta, const f
         const dim3 grid(n_seqs, n_heads, (v_dim + THREADS / SL - 1) / (THREADS / SL));                                       \
         if (grid.y > 65535 || grid.z > 65535) return SANDY_ERR_UNSUPPORTED;                                                  \
         return sandy_launch(ssm_scan_kernel<Q, SL>, grid, dim3(THREADS), 0, stream, xbc, ld, dta, d_skip, state, state_stride, \
-                            q_start, seq_slots, out, ld_out, n_heads, n_groups, state_dim, v_dim);                           \
+                            q_start, seq_slots, out, ld_out, n_heads, n_groups, state_dim, v_dim, wide);                     \
     } while (0)
-    // a thread owns at most sixteen rows of its column (eight up to a state of 128): the tokens of a request come one
-    // after another, so what a token costs is the length of a thread's chain of instructions, and the more threads
-    // share a column the shorter it is
+    // rows of B, C and x that all start on 16-byte boundaries travel sixteen bytes a copy
+    const int wide = state_dim % 4 == 0 && v_dim % 4 == 0 && ld % 4 == 0 && ((uintptr_t)xbc & 15) == 0 ? 1 : 0;
+    // a thread owns four rows of its column (eight from a state of 129 on): the tokens of a request come one after
+    // another, so what a token costs is the length of a thread's chain of instructions, and the more threads share a
+    // column the shorter it is and the more warps an SM has to choose from
     if (state_dim <= 16) SCAN(1, 4);
     if (state_dim <= 32) SCAN(1, 8);
     if (state_dim <= 64) SCAN(1, 16);
-    if (state_dim <= 128) SCAN(2, 16);
-    SCAN(4, 16);
+    if (state_dim <= 128) SCAN(1, 32);
+    SCAN(2, 32);
 #undef SCAN
 }
 
