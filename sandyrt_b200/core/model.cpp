@@ -136,16 +136,36 @@ Tensor Model::forward(StepContext& ctx) {
         cuda_check(cudaMemcpyAsync(x0.data, x.data, (size_t)x.numel() * sizeof(float), cudaMemcpyDeviceToDevice, ctx.launch.stream),
                    "keeping the embedding's output");
     }
+    ctx.owed = StepContext::OwedWrite();
+    // a block may leave its last sublayer's write into the streams owed to whoever reads them next
+    auto settle = [&](Tensor* sum_out) {
+        if (!ctx.owed.wrap) return false;
+        Wrap::Input in;
+        in.gate = ctx.owed.gate;
+        Wrap* w = ctx.owed.wrap;
+        const Tensor y = ctx.owed.y;
+        ctx.owed = StepContext::OwedWrite();
+        w->write(ctx, x, y, in, sum_out);
+        return true;
+    };
     for (const LayerCall& c : spec_.schedule) {
-        if (c.remix >= 0) remixes_[(size_t)c.remix]->forward(ctx, x, x0);
+        if (c.remix >= 0) {
+            settle(nullptr);
+            remixes_[(size_t)c.remix]->forward(ctx, x, x0);
+        }
+        if (!blocks_[(size_t)c.layer]->settles_owed()) settle(nullptr);
         blocks_[(size_t)c.layer]->forward(ctx, x, c);
     }
     if (spec_.streams > 1) {
-        ops::StreamsStep sum;                 // the final norm reads the sum of the copies
-        Tensor total = one_stream;
-        sum.sum_out = &total;
-        ops::streams_step(ctx.launch, x, spec_.streams, sum);
+        Tensor total = one_stream;            // the final norm reads the sum of the copies
+        if (!settle(&total)) {
+            ops::StreamsStep sum;
+            sum.sum_out = &total;
+            ops::streams_step(ctx.launch, x, spec_.streams, sum);
+        }
         x = one_stream;
+    } else {
+        settle(nullptr);
     }
     Tensor logits = ws.get("logits", ctx.n_rows, spec_.vocab_size, DType::F32);
     if (ctx.n_rows) {

@@ -937,7 +937,7 @@ int64_t ssm_state_floats(const SsmShape& m) { return (int64_t)m.n_heads * m.v_di
 
 void ssm_prepare(const Launch& l, const StepSeqs& s, const SsmShape& m, const Tensor& proj, const Tensor& taps, const Tensor* conv_bias,
                  const Tensor& dt_raw, const float* dt_bias, const float* a_log, const StateView& state, int64_t tail_off,
-                 Tensor& xbc, Tensor& dta) {
+                 Tensor& xbc, Tensor& dta, int max_q_len) {
     const int64_t channels = (int64_t)m.n_heads * m.v_dim + 2 * (int64_t)m.n_groups * m.state;
     if (proj.cols != channels || proj.rows != s.n_tokens || taps.dtype != DType::F32 || taps.numel() != channels * m.n_taps ||
         (conv_bias && (conv_bias->dtype != DType::F32 || conv_bias->numel() != channels)) || dt_raw.dtype != DType::F32 ||
@@ -949,9 +949,10 @@ void ssm_prepare(const Launch& l, const StepSeqs& s, const SsmShape& m, const Te
     OpTimer timer(l, "state space: conv + gates", tensor_bytes(&proj) + tensor_bytes(&xbc), 0);
     check(fn(proj.data, (int)proj.ld, code_of(proj.dtype), (int)channels, (const float*)taps.data, m.n_taps,
              conv_bias ? (const float*)conv_bias->data : nullptr, (const float*)dt_raw.data, (int)dt_raw.ld, dt_bias, a_log, m.n_heads,
-             (const float*)state.data, state.row_elems, tail_off, s.token_seq, s.q_start, s.seq_slots, (float*)xbc.data, (int)xbc.ld,
-             (float*)dta.data, s.n_tokens, l.stream),
+             (float*)state.data, state.row_elems, tail_off, s.token_seq, s.q_start, s.seq_slots, (float*)xbc.data, (int)xbc.ld,
+             (float*)dta.data, s.n_tokens, max_q_len <= 1 ? 1 : 0, l.stream),
           "ssm_prepare");
+    if (max_q_len > 1) conv_tail(l, s, proj, m.n_taps, state, tail_off);
 }
 
 void ssm_scan(const Launch& l, const StepSeqs& s, const SsmShape& m, const Tensor& xbc, const Tensor& dta, const float* d_skip,

@@ -320,10 +320,11 @@ struct SsmShape { int n_heads = 0, n_groups = 0, state = 0, v_dim = 0, n_taps = 
 int64_t ssm_state_floats(const SsmShape& m);                       // S [H][P][N]; the convolution's tail follows it
 // proj: the x, B and C channels ([T, H * P + 2 G * N], a column range of the input projection); taps float32 [channels,
 // n_taps], conv_bias float32 [channels] or null; dt_raw float32 [T, H]; xbc float32 [T, channels] = silu(conv + bias);
-// dta float32 [T, 2H]: dt = softplus(raw + dt_bias), then -exp(a_log) dt.
+// dta float32 [T, 2H]: dt = softplus(raw + dt_bias), then -exp(a_log) dt.  The convolution's tail in the state moves on by
+// the step's tokens: in the same launch when the step's longest portion `max_q_len` is one token, by conv_tail otherwise.
 void ssm_prepare(const Launch& l, const StepSeqs& s, const SsmShape& m, const Tensor& proj, const Tensor& taps, const Tensor* conv_bias,
                  const Tensor& dt_raw, const float* dt_bias, const float* a_log, const StateView& state, int64_t tail_off,
-                 Tensor& xbc, Tensor& dta);
+                 Tensor& xbc, Tensor& dta, int max_q_len);
 // S <- exp(dta[1]) S + dt B x^T; out = S^T C + d_skip x, float32 [T, H * P]; d_skip float32 [H] or null.
 void ssm_scan(const Launch& l, const StepSeqs& s, const SsmShape& m, const Tensor& xbc, const Tensor& dta, const float* d_skip,
               const StateView& state, Tensor& out);

@@ -47,6 +47,7 @@
 namespace sandy {
 
 class PositionEncoding;
+class Wrap;
 
 // Everything a part may read about the running step.  Device arrays are int32.
 struct StepContext {
@@ -65,6 +66,10 @@ struct StepContext {
     DeviceCaches* caches = nullptr;
     PositionEncoding* position = nullptr;    // the model's position encoding
     int embedding_cache = -1;                // the cache entry of the embedding's own state per request, or -1
+    // A sublayer's result that its wrap has not written into the streams yet.  A block whose last sublayer sits in a wrap
+    // may leave the write owed; whoever reads the streams next (the next block's first wrap, or the model before a stream
+    // mix and before its final norm) does it in its own pass over them.  `y` and `gate` stay untouched until then.
+    struct OwedWrite { Wrap* wrap = nullptr; Tensor y, gate; } owed;
     // Set by a block that norms a sublayer's output before it joins the stream: a mixer or feed-forward that
     // says `can_overwrite()` then writes its result over the tensor it is given instead of adding to it.
     bool overwrite = false;
@@ -199,8 +204,9 @@ public:
     // first, in the same pass over the streams.
     virtual Input read(StepContext& ctx, Tensor& X, const StateView* state, int64_t offset, Wrap* before, const Tensor* before_y,
                        const Input* before_in) = 0;
-    // X <- the streams with the sublayer's result y (float32 [tokens, width]) joined.
-    virtual void write(StepContext& ctx, Tensor& X, const Tensor& y, const Input& in) = 0;
+    // X <- the streams with the sublayer's result y (float32 [tokens, width]) joined; with `sum_out` (float32 [tokens,
+    // width]) also the sum of the streams after that.
+    virtual void write(StepContext& ctx, Tensor& X, const Tensor& y, const Input& in, Tensor* sum_out = nullptr) = 0;
 };
 
 // An arrangement of norms, a mixer and a feed-forward (built from a LayerSpec).
@@ -213,6 +219,9 @@ public:
     virtual void forward(StepContext& ctx, Tensor& x, const LayerCall& call) = 0;
     // What the layer asks of the cache manager: the mixer's needs, plus whatever the block itself keeps per request.
     virtual CacheSpec cache_spec() const { return mixer_->cache_spec(); }
+    // Whether `forward` itself does a write into the streams that the block before left owed (StepContext::owed); the
+    // model settles it in front of every block that does not.
+    virtual bool settles_owed() const { return false; }
     Mixer& mixer() { return *mixer_; }
     FeedForward& feed_forward() { return *ff_; }
     std::map<std::string, std::unique_ptr<Norm>>& norms() { return norms_; }

@@ -159,9 +159,10 @@ public:
         gate_lin_.run(ctx, nullptr, &h, out.gate, ops::Act::None, nullptr);
         return out;
     }
-    void write(StepContext& ctx, Tensor& X, const Tensor& y, const Input& in) override {
+    void write(StepContext& ctx, Tensor& X, const Tensor& y, const Input& in, Tensor* sum_out) override {
         ops::StreamsStep st;
         fill_write(st, &y, &in);
+        st.sum_out = sum_out;
         ops::streams_step(ctx.launch, X, S_, st);
     }
 private:
@@ -196,6 +197,7 @@ public:
         }
         return CacheSpec::state({own + extra});
     }
+    bool settles_owed() const override { return true; }
     void forward(StepContext& ctx, Tensor& X, const LayerCall& call) override {
         Wrap& w1 = *wraps_.at("mixer");
         Wrap* w2 = ff_->empty() ? nullptr : wraps_.at("feed_forward").get();
@@ -204,8 +206,13 @@ public:
         StateView state;
         if (stateful) state = ctx.caches->state(call.cache);
         const StateView* sv = stateful ? &state : nullptr;
+        // the write that the block before left owed rides in this block's first pass over the streams
+        StepContext::OwedWrite owed = ctx.owed;
+        ctx.owed = StepContext::OwedWrite();
+        Wrap::Input owed_in;
+        owed_in.gate = owed.gate;
+        Wrap::Input in1 = w1.read(ctx, X, sv, own, owed.wrap, owed.wrap ? &owed.y : nullptr, owed.wrap ? &owed_in : nullptr);
         Tensor y = ctx.workspace->get("branch", X.rows, width_, DType::F32);
-        Wrap::Input in1 = w1.read(ctx, X, sv, own, nullptr, nullptr, nullptr);
         {
             NormedInput h(ctx, in1.sublayer_in);
             begin_branch(ctx, y, mixer_->can_overwrite());
@@ -213,7 +220,7 @@ public:
             ctx.overwrite = false;
         }
         if (!w2) {
-            w1.write(ctx, X, y, in1);
+            leave_owed(ctx, w1, y, in1);
             return;
         }
         Wrap::Input in2 = w2->read(ctx, X, sv, own + w1.state_floats(), &w1, &y, &in1);
@@ -223,9 +230,16 @@ public:
             ff_->forward(ctx, h, y);
             ctx.overwrite = false;
         }
-        w2->write(ctx, X, y, in2);
+        leave_owed(ctx, *w2, y, in2);
     }
 private:
+    // The last sublayer's write waits for the next pass over the streams (StepContext::owed): its result and its gate sit
+    // in workspace buffers that nothing touches before that pass has read them.
+    static void leave_owed(StepContext& ctx, Wrap& w, const Tensor& y, const Wrap::Input& in) {
+        ctx.owed.wrap = &w;
+        ctx.owed.y = y;
+        ctx.owed.gate = in.gate;
+    }
     static void begin_branch(StepContext& ctx, Tensor& y, bool overwrites) {
         ctx.overwrite = overwrites;
         if (!overwrites)
@@ -419,8 +433,7 @@ public:
         Tensor xbc = ws.get("ssm_xbc", T, channels_, DType::F32);
         Tensor dta = ws.get("ssm_dt", T, 2 * H_, DType::F32);
         ops::ssm_prepare(l, seqs, m, xbc_in, conv_.view, &conv_bias_.view, dt_raw, (const float*)dt_bias_.view.data,
-                         (const float*)a_log_.view.data, state, tail_off, xbc, dta);
-        ops::conv_tail(l, seqs, xbc_in, taps_, state, tail_off);
+                         (const float*)a_log_.view.data, state, tail_off, xbc, dta, ctx.max_q_len);
         Tensor read = ws.get("mix_read", T, inner_, DType::F32);
         ops::ssm_scan(l, seqs, m, xbc, dta, (const float*)d_.view.data, state, read);
         Tensor normed = ws.get("ssm_normed", T, inner_, ctx.compute_dtype);

@@ -690,14 +690,16 @@ def embed_bigram(ids, positions, token_seq, q_start, seq_slots, wte, bigram, wpe
                                      ctypes.c_int(seq_slots.numel()), _stream()), "bigram_keep")
 
 
-def ssm_prepare(proj, taps, conv_bias, dt_raw, dt_bias, a_log, state, tail_off: int, token_seq, q_start, seq_slots, xbc, dta) -> None:
-    """xbc = silu(causal conv(proj) + conv_bias), float32; dta = (softplus(dt_raw + dt_bias), -exp(a_log) * that), float32 [T, 2H]."""
+def ssm_prepare(proj, taps, conv_bias, dt_raw, dt_bias, a_log, state, tail_off: int, token_seq, q_start, seq_slots, xbc, dta, *,
+                keep: bool = False) -> None:
+    """xbc = silu(causal conv(proj) + conv_bias), float32; dta = (softplus(dt_raw + dt_bias), -exp(a_log) * that), float32 [T, 2H].
+    With keep (steps of single tokens) the convolution's tails move on in the same launch; otherwise conv_tail follows."""
     _cuda(proj, taps, conv_bias, dt_raw, dt_bias, a_log, state, token_seq, q_start, seq_slots, xbc, dta)
     code = load_library("ssm_state").sandy_ssm_prepare(
         _p(proj), ctypes.c_int(proj.stride(0)), ctypes.c_int(_dt(proj)), ctypes.c_int(proj.shape[1]), _p(taps), ctypes.c_int(taps.shape[1]),
         _p(conv_bias), _p(dt_raw), ctypes.c_int(dt_raw.stride(0)), _p(dt_bias), _p(a_log), ctypes.c_int(dt_raw.shape[1]), _p(state),
         ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(tail_off), _p(token_seq), _p(q_start), _p(seq_slots), _p(xbc),
-        ctypes.c_int(xbc.stride(0)), _p(dta), ctypes.c_int(proj.shape[0]), _stream())
+        ctypes.c_int(xbc.stride(0)), _p(dta), ctypes.c_int(proj.shape[0]), ctypes.c_int(1 if keep else 0), _stream())
     _check(code, "ssm_prepare")
 
 

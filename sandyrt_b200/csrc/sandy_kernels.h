@@ -306,9 +306,9 @@ int sandy_bigram_keep(const int* ids, const int* q_start, const int* seq_slots, 
 /* ssm_state.cu */
 long long sandy_ssm_state_floats(int n_heads, int state, int v_dim);
 int sandy_ssm_prepare(const void* proj, int ld, int dtype, int channels, const float* taps, int n_taps, const float* conv_bias,
-                      const float* dt_raw, int ld_dt, const float* dt_bias, const float* a_log, int n_heads, const float* state,
+                      const float* dt_raw, int ld_dt, const float* dt_bias, const float* a_log, int n_heads, float* state,
                       long long state_stride, long long tail_off, const int* token_seq, const int* q_start, const int* seq_slots,
-                      float* xbc, int ld_xbc, float* dta, int n_tokens, cudaStream_t stream);
+                      float* xbc, int ld_xbc, float* dta, int n_tokens, int keep, cudaStream_t stream);
 int sandy_ssm_scan(const float* xbc, int ld, const float* dta, const float* d_skip, float* state, long long state_stride,
                    const int* q_start, const int* seq_slots, float* out, int ld_out, int n_seqs, int n_heads, int n_groups,
                    int state_dim, int v_dim, cudaStream_t stream);

@@ -34,13 +34,13 @@ __global__ void __launch_bounds__(256)
 ssm_prepare_kernel(const T* __restrict__ proj, int ld, int channels, const float* __restrict__ taps, int n_taps,
                    const float* __restrict__ conv_bias, const float* __restrict__ dt_raw, int ld_dt,
                    const float* __restrict__ dt_bias, const float* __restrict__ a_log, int n_heads,
-                   const float* __restrict__ state, long long state_stride, long long tail_off,
+                   float* __restrict__ state, long long state_stride, long long tail_off,
                    const int* __restrict__ token_seq, const int* __restrict__ q_start, const int* __restrict__ seq_slots,
-                   float* __restrict__ xbc, int ld_xbc, float* __restrict__ dta) {
+                   float* __restrict__ xbc, int ld_xbc, float* __restrict__ dta, int keep) {
     const int t = blockIdx.x;
     const int s = token_seq[t];
     const int i_in_step = t - q_start[s];
-    const float* tail = state + (long long)seq_slots[s] * state_stride + tail_off;      // [n_taps - 1][channels]
+    float* tail = state + (long long)seq_slots[s] * state_stride + tail_off;      // [n_taps - 1][channels]
     pdl_wait();
     pdl_launch_dependents();
     for (int c = threadIdx.x; c < channels; c += blockDim.x) {
@@ -52,6 +52,11 @@ ssm_prepare_kernel(const T* __restrict__ proj, int ld, int channels, const float
             y = fmaf(taps[(size_t)c * n_taps + j], x, y);
         }
         xbc[(size_t)t * ld_xbc + c] = silu_f(y);
+        // a step of single tokens: the tail moves on by this token here (this thread alone reads and writes its channel)
+        if (keep && n_taps > 1) {
+            for (int j = 0; j + 2 < n_taps; j++) tail[(size_t)j * channels + c] = tail[(size_t)(j + 1) * channels + c];
+            tail[(size_t)(n_taps - 2) * channels + c] = to_f32(proj[(size_t)t * ld + c]);
+        }
     }
     for (int h = threadIdx.x; h < n_heads; h += blockDim.x) {
         const float dt = softplus_f(dt_raw[(size_t)t * ld_dt + h] + dt_bias[h]);
@@ -240,12 +245,13 @@ SANDY_API long long sandy_ssm_state_floats(int n_heads, int state, int v_dim) { 
 // proj: [n_tokens, >= channels] of dtype with pitch ld, the x, B and C channels first (the caller passes the address of
 // their first column).  taps float32 [channels, n_taps], conv_bias float32 [channels] or null.  dt_raw float32
 // [n_tokens, >= n_heads] with pitch ld_dt.  The tail of a slot is float32 [n_taps - 1][channels] at tail_off of its state.
-// xbc float32 [n_tokens, channels] with pitch ld_xbc; dta float32 [n_tokens, 2 * n_heads].
+// xbc float32 [n_tokens, channels] with pitch ld_xbc; dta float32 [n_tokens, 2 * n_heads].  keep != 0 (only right when every
+// request brings one token): the tails move on by the step's tokens in this launch; otherwise sandy_conv_tail follows.
 SANDY_API int sandy_ssm_prepare(const void* proj, int ld, int dtype, int channels, const float* taps, int n_taps,
                                 const float* conv_bias, const float* dt_raw, int ld_dt, const float* dt_bias, const float* a_log,
-                                int n_heads, const float* state, long long state_stride, long long tail_off,
+                                int n_heads, float* state, long long state_stride, long long tail_off,
                                 const int* token_seq, const int* q_start, const int* seq_slots, float* xbc, int ld_xbc,
-                                float* dta, int n_tokens, cudaStream_t stream) {
+                                float* dta, int n_tokens, int keep, cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (!proj || !taps || !dt_raw || !dt_bias || !a_log || !token_seq || !q_start || !seq_slots || !xbc || !dta ||
         (n_taps > 1 && !state))
@@ -254,11 +260,11 @@ SANDY_API int sandy_ssm_prepare(const void* proj, int ld, int dtype, int channel
     if (dtype == SANDY_F32)
         return sandy_launch(ssm_prepare_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)proj, ld, channels, taps,
                             n_taps, conv_bias, dt_raw, ld_dt, dt_bias, a_log, n_heads, state, state_stride, tail_off, token_seq,
-                            q_start, seq_slots, xbc, ld_xbc, dta);
+                            q_start, seq_slots, xbc, ld_xbc, dta, keep);
     if (dtype == SANDY_BF16)
         return sandy_launch(ssm_prepare_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, (const bf16*)proj, ld, channels, taps,
                             n_taps, conv_bias, dt_raw, ld_dt, dt_bias, a_log, n_heads, state, state_stride, tail_off, token_seq,
-                            q_start, seq_slots, xbc, ld_xbc, dta);
+                            q_start, seq_slots, xbc, ld_xbc, dta, keep);
     return SANDY_ERR_UNSUPPORTED;
 }
 

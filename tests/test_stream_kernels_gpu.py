@@ -249,8 +249,9 @@ def test_the_recurrence_in_portions_and_single_tokens(H, G, N, P, taps, dtype):
         slots = torch.tensor([slots_all[r] for r in who], dtype=torch.int32, device=DEV)
         T = starts[-1]
         xbc, dta, out = torch.zeros(T, ch, device=DEV), torch.zeros(T, 2 * H, device=DEV), torch.zeros(T, inner, device=DEV)
-        ops.ssm_prepare(x, w, cb, raw, dt_bias, a_log, state, tail_off, token_seq, q_start, slots, xbc, dta)
-        if taps > 1:
+        single = max(n_of.values()) == 1            # a step of single tokens keeps its tails itself
+        ops.ssm_prepare(x, w, cb, raw, dt_bias, a_log, state, tail_off, token_seq, q_start, slots, xbc, dta, keep=single)
+        if taps > 1 and not single:
             ops.conv_tail(x, taps, state, tail_off, q_start, slots)
         ops.ssm_scan(xbc, dta, d_skip, state, q_start, slots, out, n_heads=H, n_groups=G, state_dim=N, v_dim=P)
         for i, r in enumerate(who):
