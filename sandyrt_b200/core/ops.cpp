@@ -946,12 +946,14 @@ void ssm_prepare(const Launch& l, const StepSeqs& s, const SsmShape& m, const Te
         state.dtype != DType::F32 || tail_off + (int64_t)(m.n_taps - 1) * channels > state.row_elems)
         throw KernelError("ssm_prepare: shapes disagree");
     static auto fn = SANDY_KERNEL(ssm_state, sandy_ssm_prepare);
-    OpTimer timer(l, "state space: conv + gates", tensor_bytes(&proj) + tensor_bytes(&xbc), 0);
-    check(fn(proj.data, (int)proj.ld, code_of(proj.dtype), (int)channels, (const float*)taps.data, m.n_taps,
-             conv_bias ? (const float*)conv_bias->data : nullptr, (const float*)dt_raw.data, (int)dt_raw.ld, dt_bias, a_log, m.n_heads,
-             (float*)state.data, state.row_elems, tail_off, s.token_seq, s.q_start, s.seq_slots, (float*)xbc.data, (int)xbc.ld,
-             (float*)dta.data, s.n_tokens, max_q_len <= 1 ? 1 : 0, l.stream),
-          "ssm_prepare");
+    {
+        OpTimer timer(l, "state space: conv + gates", tensor_bytes(&proj) + tensor_bytes(&xbc), 0);
+        check(fn(proj.data, (int)proj.ld, code_of(proj.dtype), (int)channels, (const float*)taps.data, m.n_taps,
+                 conv_bias ? (const float*)conv_bias->data : nullptr, (const float*)dt_raw.data, (int)dt_raw.ld, dt_bias, a_log,
+                 m.n_heads, (float*)state.data, state.row_elems, tail_off, s.token_seq, s.q_start, s.seq_slots, (float*)xbc.data,
+                 (int)xbc.ld, (float*)dta.data, s.n_tokens, max_q_len <= 1 ? 1 : 0, l.stream),
+              "ssm_prepare");
+    }
     if (max_q_len > 1) conv_tail(l, s, proj, m.n_taps, state, tail_off);
 }
 
