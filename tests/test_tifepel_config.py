@@ -141,9 +141,9 @@ def test_cache_layout_has_pages_and_states():
 
 # ---- the plain implementation --------------------------------------------------------------------------------------
 def test_plain_buckets():
-    rows, far = 32, 240
+    rows, far = 24, 150
     b = [plain.distance_bucket(n, rows, far) for n in range(400)]
-    assert b[:16] == list(range(16)) and b[16] == 16 and b[far] == rows - 1 and b[399] == rows - 1
+    assert b[:12] == list(range(12)) and b[12] == 12 and b[far] == rows - 1 and b[399] == rows - 1
     assert all(y >= x for x, y in zip(b, b[1:])) and set(b) == set(range(rows))
     assert plain.distance_bucket(1, 2, 2) == 1 and plain.distance_bucket(0, 2, 2) == 0
 

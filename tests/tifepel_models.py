@@ -46,7 +46,7 @@ def layer(mixer: dict, mlp: Optional[dict]) -> dict:
     return out
 
 
-def _config(vocab, width, layers, streams=2, taps=3, eps=1e-5, max_positions=512, bigram=(31, 7, 3), loop=None):
+def _config(vocab, width, layers, streams=2, taps=4, eps=1e-5, max_positions=512, bigram=(31, 7, 3), loop=None):
     c = {"architecture": "Tifepel", "vocab": vocab, "width": width, "max_positions": max_positions, "streams": streams,
          "norm": {"eps": eps}, "canon": {"taps": taps},
          "embedding": {"bigram": {"buckets": bigram[0], "mul_prev": bigram[1], "mul_cur": bigram[2]}}, "layers": layers}
@@ -78,7 +78,7 @@ CONFIG_B = _config(77, 100, [
 CONFIG_C = _config(311, 128, [
     layer(attention(8, 1, 64, 64, rows=32, far=100, every=32, coef=0.5), moe(20, 12, 6, 32, shared=64)),
     layer(mamba2(2, 1, 128, 64, conv=4, norm_groups=2), moe(8, 8, 4, 48, shared=16)),
-], streams=4, taps=4, eps=1e-5, bigram=(509, 127, 17), loop=(0, 2, 3))
+], streams=4, taps=4, eps=1e-5, bigram=(499, 131, 19), loop=(0, 2, 3))
 
 CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
 
