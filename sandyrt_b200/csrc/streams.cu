@@ -207,7 +207,10 @@ embed_bigram_kernel(const int* __restrict__ ids, const int* __restrict__ positio
         for (int j = threadIdx.x; j < width; j += THREADS) x[(size_t)t * ldx + j] = 0.0f;
         return;
     }
-    const long long brow = pos == 0 ? (long long)buckets : ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+    // ids and multipliers are below 2^31 each: the sum of the two products stays below 2^63, which unsigned 64-bit arithmetic holds
+    const long long brow = pos == 0 ? (long long)buckets
+                                    : (long long)(((unsigned long long)prev * (unsigned long long)mul_prev +
+                                                   (unsigned long long)id * (unsigned long long)mul_cur) % (unsigned long long)buckets);
     const T* e = wte + (size_t)id * width;
     const T* b = bigram + (size_t)brow * width;
     const T* p = wpe ? wpe + (size_t)pos * width : nullptr;
