@@ -639,17 +639,21 @@ def moe_combine_identity(r: Routing, n_real: int, h, rows, y, *, add: bool) -> N
 
 # ---- a residual stream in several copies; a state-space mixer (streams.cu, ssm_state.cu) ---------------------------
 def streams_step(X, n_streams: int, *, y=None, gate=None, gate_bias=None, mix=None, out_w=None, in_w=None, gain=None, eps: float = 0.0,
-                 h=None, sum_out=None) -> None:
+                 h=None, sum_out=None, taps=None, state=None, tail_off: int = 0, token_seq=None, seq_slots=None, conv_out=None) -> None:
     """One pass over the streams X (float32 [T, S * width], in place), each part optional and in this order: the write
     X_t <- sum_s mix[s, t] X_s + out_w[t] * y * sigmoid(gate + gate_bias); sum_out = sum_s X_s; the read
-    h = LayerNorm(sum_s in_w[s] X_s) * gain without an offset."""
-    _cuda(X, y, gate, gate_bias, mix, out_w, in_w, gain, h, sum_out)
+    h = LayerNorm(sum_s in_w[s] X_s) * gain without an offset.  With `taps` (only in a step in which every request brings
+    one token): conv_out = h + conv(h) as canon_conv gives it, and the request's tail in `state` moved on by the token."""
+    _cuda(X, y, gate, gate_bias, mix, out_w, in_w, gain, h, sum_out, taps, state, token_seq, seq_slots, conv_out)
     T, W = X.shape[0], X.shape[1] // n_streams
-    code = load_library("streams").sandy_streams_step(
+    code = load_library("streams").sandy_streams_step_conv(
         _p(X), ctypes.c_int(X.stride(0)), ctypes.c_int(T), ctypes.c_int(n_streams), ctypes.c_int(W), _p(y),
         ctypes.c_int(0 if y is None else y.stride(0)), _p(gate), ctypes.c_int(0 if gate is None else gate.stride(0)), _p(gate_bias),
         _p(mix), _p(out_w), _p(in_w), _p(gain), ctypes.c_float(eps), _p(h), ctypes.c_int(0 if h is None else h.stride(0)),
-        ctypes.c_int(0 if h is None else _dt(h)), _p(sum_out), ctypes.c_int(0 if sum_out is None else sum_out.stride(0)), _stream())
+        ctypes.c_int(0 if h is None else _dt(h)), _p(sum_out), ctypes.c_int(0 if sum_out is None else sum_out.stride(0)),
+        _p(taps), ctypes.c_int(0 if taps is None else taps.shape[1]), _p(state), ctypes.c_longlong(0 if state is None else state.stride(0)),
+        ctypes.c_longlong(tail_off), _p(token_seq), _p(seq_slots), _p(conv_out), ctypes.c_int(0 if conv_out is None else conv_out.stride(0)),
+        _stream())
     _check(code, f"streams_step(S={n_streams},width={W})")
 
 

@@ -27,14 +27,15 @@
 namespace {
 
 constexpr int THREADS = 256;
+constexpr int BIG = 1024;                       // threads of a block when a step has few tokens
 constexpr int MAX_STREAMS = 8;
 constexpr int MAX_PER_THREAD = 8;              // channels a thread keeps in registers: widths up to 2,048
 constexpr int MAX_TAPS = 8;
 
-// One token's row.  PER > 0: width <= PER * THREADS and the streams stay in registers; PER == 0: any width, the streams
-// are read again where they are needed (they were written by this thread, so no barrier lies between).
-template <typename T, int S_MAX, int PER>
-__global__ void __launch_bounds__(THREADS)
+// One token's row on TH threads.  PER > 0: width <= PER * TH and the streams stay in registers; PER == 0: any width, the
+// streams are read again where they are needed (they were written by this thread, so no barrier lies between).
+template <typename T, int S_MAX, int PER, int TH>
+__global__ void __launch_bounds__(TH)
 streams_step_kernel(float* __restrict__ X, int ldX, int n_streams, int width,
                     const float* __restrict__ y, int ldy, const float* __restrict__ gate, int ldg,
                     const float* __restrict__ gate_bias, const float* __restrict__ mix, const float* __restrict__ out_w,
@@ -47,7 +48,7 @@ streams_step_kernel(float* __restrict__ X, int ldX, int n_streams, int width,
     const int t = blockIdx.x;
     const int S = n_streams;
     // the small tables are weights: they may be read before the kernel in front has ended
-    for (int i = threadIdx.x; i < S * S + 2 * S; i += THREADS) {
+    for (int i = threadIdx.x; i < S * S + 2 * S; i += TH) {
         float v = 0.0f;
         if (i < S * S) v = mix ? mix[i] : 0.0f;
         else if (i < S * S + S) v = out_w ? out_w[i - S * S] : 0.0f;
@@ -61,9 +62,9 @@ streams_step_kernel(float* __restrict__ X, int ldX, int n_streams, int width,
     constexpr int P = PER > 0 ? PER : 1;
     float u[P];
     float total = 0.0f;
-    const int rounds = PER > 0 ? PER : (width + THREADS - 1) / THREADS;
+    const int rounds = PER > 0 ? PER : (width + TH - 1) / TH;
     for (int r = 0; r < rounds; r++) {
-        const int j = threadIdx.x + r * THREADS;
+        const int j = threadIdx.x + r * TH;
         float uj = 0.0f;
         if (j < width) {
             float x[S_MAX];
@@ -116,7 +117,7 @@ streams_step_kernel(float* __restrict__ X, int ldX, int n_streams, int width,
     const float mean = block_sum(total, scratch) / (float)width;
     float sq = 0.0f;
     for (int r = 0; r < rounds; r++) {
-        const int j = threadIdx.x + r * THREADS;
+        const int j = threadIdx.x + r * TH;
         if (j < width) {
             const float d = u_at(r, j) - mean;
             sq = fmaf(d, d, sq);
@@ -127,7 +128,7 @@ streams_step_kernel(float* __restrict__ X, int ldX, int n_streams, int width,
     // moves on by this token (a thread owns its channels of the tail: nobody else reads or writes them in this step).
     float* tail = taps && n_taps > 1 ? state + (long long)seq_slots[token_seq[t]] * state_stride + tail_off : nullptr;
     for (int r = 0; r < rounds; r++) {
-        const int j = threadIdx.x + r * THREADS;
+        const int j = threadIdx.x + r * TH;
         if (j < width) {
             const T rounded = from_f32<T>((u_at(r, j) - mean) * rstd * gain[j]);
             h[(size_t)t * ldh + j] = rounded;
@@ -241,23 +242,31 @@ int launch_step(float* X, int ldX, int n_tokens, int S, int width, const float* 
                 const float* gate_bias, const float* mix, const float* out_w, const float* in_w, const float* gain, float eps,
                 T* h, int ldh, float* sum_out, int ld_sum, const float* taps, int n_taps, float* state, long long state_stride,
                 long long tail_off, const int* token_seq, const int* seq_slots, T* c, int ldc, cudaStream_t stream) {
-#define STEP(SM, PER)                                                                                                        \
-    return sandy_launch(streams_step_kernel<T, SM, PER>, dim3(n_tokens), dim3(THREADS), 0, stream, X, ldX, S, width, y, ldy, \
+#define STEP(SM, PER, TH)                                                                                                    \
+    return sandy_launch(streams_step_kernel<T, SM, PER, TH>, dim3(n_tokens), dim3(TH), 0, stream, X, ldX, S, width, y, ldy,  \
                         gate, ldg, gate_bias, mix, out_w, in_w, gain, eps, h, ldh, sum_out, ld_sum, taps, n_taps, state,      \
                         state_stride, tail_off, token_seq, seq_slots, c, ldc)
+    // A step of few tokens (a decode step) leaves most SMs without a block: a token's row then goes over 1,024 threads, a
+    // channel or two each, so that the chain of loads and the two sums a thread walks is short.  Many tokens: 256 threads.
+    const bool few = n_tokens < sandy_sm_count() && width > THREADS;
     if (S <= 2) {
-        if (width <= 2 * THREADS) STEP(2, 2);
-        if (width <= 4 * THREADS) STEP(2, 4);
-        if (width <= MAX_PER_THREAD * THREADS) STEP(2, MAX_PER_THREAD);
-        STEP(2, 0);
+        if (few && width <= BIG) STEP(2, 1, BIG);
+        if (few && width <= 2 * BIG) STEP(2, 2, BIG);
+        if (width <= 2 * THREADS) STEP(2, 2, THREADS);
+        if (width <= 4 * THREADS) STEP(2, 4, THREADS);
+        if (width <= MAX_PER_THREAD * THREADS) STEP(2, MAX_PER_THREAD, THREADS);
+        STEP(2, 0, THREADS);
     }
     if (S <= 4) {
-        if (width <= 4 * THREADS) STEP(4, 4);
-        if (width <= MAX_PER_THREAD * THREADS) STEP(4, MAX_PER_THREAD);
-        STEP(4, 0);
+        if (few && width <= BIG) STEP(4, 1, BIG);
+        if (few && width <= 2 * BIG) STEP(4, 2, BIG);
+        if (width <= 4 * THREADS) STEP(4, 4, THREADS);
+        if (width <= MAX_PER_THREAD * THREADS) STEP(4, MAX_PER_THREAD, THREADS);
+        STEP(4, 0, THREADS);
     }
-    if (width <= 4 * THREADS) STEP(MAX_STREAMS, 4);
-    STEP(MAX_STREAMS, 0);
+    if (few && width <= BIG) STEP(MAX_STREAMS, 1, BIG);
+    if (width <= 4 * THREADS) STEP(MAX_STREAMS, 4, THREADS);
+    STEP(MAX_STREAMS, 0, THREADS);
 #undef STEP
 }
 

@@ -115,12 +115,13 @@ def _layer_norm(u, gain, eps):
     return d / torch.sqrt((d * d).mean(-1, keepdim=True) + eps) * gain
 
 
-@pytest.mark.parametrize("S,W", [(1, 48), (2, 328), (3, 100), (4, 1024), (8, 64), (2, 2500), (5, 1536)])
+@pytest.mark.parametrize("T", [37, 300])
+@pytest.mark.parametrize("S,W", [(1, 48), (2, 328), (3, 100), (4, 1024), (8, 64), (2, 2500), (5, 1536), (8, 900), (4, 2048)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_a_pass_over_the_streams(S, W, dtype):
-    """Write, sum and read in one launch and each alone; widths that keep the streams in registers and widths beyond."""
+def test_a_pass_over_the_streams(S, W, dtype, T):
+    """Write, sum and read in one launch and each alone; widths that keep the streams in registers and widths beyond; few
+    tokens (a row over 1,024 threads) and many (256 threads)."""
     g = torch.Generator().manual_seed(S * 1000 + W)
-    T = 37
     X0 = torch.randn(T, S * W, generator=g).to(DEV)
     y, gate = torch.randn(T, W, generator=g).to(DEV), torch.randn(T, W, generator=g).to(DEV)
     gate_bias, gain = torch.randn(W, generator=g).to(DEV), (1 + 0.2 * torch.randn(W, generator=g)).to(DEV)
@@ -144,6 +145,37 @@ def test_a_pass_over_the_streams(S, W, dtype):
     assert torch.equal(X, X0)
     want0 = _layer_norm(torch.einsum("s,nsw->nw", in_w.double(), Xs), gain.double(), 1e-5)
     assert (h.double() - want0).abs().max().item() < tol * max(1.0, want0.abs().max().item())
+
+
+@pytest.mark.parametrize("S,W,taps", [(2, 40, 3), (4, 1536, 4), (3, 1000, 1), (8, 300, 8), (1, 2100, 2)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_convolution_inside_the_pass_in_steps_of_single_tokens(S, W, taps, dtype):
+    """Five steps of one token for each of three requests: the pass that reads the streams also runs the convolution and
+    moves the tails on; the same rows through the convolution's own kernel and conv_tail are the measure."""
+    g = torch.Generator().manual_seed(S + W + taps)
+    off = 5
+    slots = torch.tensor([3, 0, 1], dtype=torch.int32, device=DEV)
+    token_seq = torch.arange(3, dtype=torch.int32, device=DEV)
+    q_start = torch.arange(4, dtype=torch.int32, device=DEV)
+    w = torch.randn(W, taps, generator=g).to(DEV)
+    in_w, gain = torch.randn(S, generator=g).to(DEV), (1 + 0.2 * torch.randn(W, generator=g)).to(DEV)
+    state_a = torch.zeros(4, off + (taps - 1) * W + 3, device=DEV)
+    state_b = state_a.clone()
+    for step in range(5):
+        X = torch.randn(3, S * W, generator=g).to(DEV)
+        h_a, c_a = torch.zeros(3, W, dtype=dtype, device=DEV), torch.zeros(3, W, dtype=dtype, device=DEV)
+        ops.streams_step(X.clone(), S, in_w=in_w, gain=gain, eps=1e-5, h=h_a, taps=w, state=state_a, tail_off=off, token_seq=token_seq,
+                         seq_slots=slots, conv_out=c_a)
+        h_b, c_b = torch.zeros_like(h_a), torch.zeros_like(c_a)
+        ops.streams_step(X.clone(), S, in_w=in_w, gain=gain, eps=1e-5, h=h_b)
+        ops.canon_conv(h_b, w, state_b, off, token_seq, q_start, slots, c_b)
+        if taps > 1:
+            ops.conv_tail(h_b, taps, state_b, off, q_start, slots)
+        assert torch.equal(h_a, h_b), f"step {step}"
+        tol = 1e-5 if dtype == torch.float32 else 0.07
+        assert (c_a.float() - c_b.float()).abs().max().item() < tol * max(1.0, c_b.float().abs().max().item()), f"step {step}"
+        assert torch.equal(state_a, state_b), f"step {step}: the tails differ"
+    assert state_a[2].abs().max().item() == 0.0 and (taps == 1 or state_a[3, off:].abs().max().item() > 0.0)
 
 
 @pytest.mark.parametrize("taps", [1, 2, 3, 8])
